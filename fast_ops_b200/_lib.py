@@ -1,0 +1,95 @@
+"""Loads the C-ABI library (libfast_ops_b200.so) and declares its entry points for ctypes.
+
+There is no fallback: if the library is missing and cannot be built, or a call fails, the
+caller gets a RuntimeError.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libfast_ops_b200.so")
+
+FO_F16, FO_BF16, FO_F32 = 0, 1, 2
+
+_lock = threading.Lock()
+_lib = None
+
+_c = ctypes
+_PTR = _c.c_void_p
+_I64P = _c.POINTER(_c.c_int64)
+
+# name -> (restype, argtypes); mirrors include/fast_ops_b200.h
+SIGNATURES = {
+    "fo_version": (_c.c_int, []),
+    "fo_last_error": (_c.c_char_p, []),
+    "fo_device_status": (_c.c_int, [_c.c_int, _c.POINTER(_c.c_int), _c.c_int]),
+    "fo_flash_attn_fwd": (_c.c_int, [_PTR, _PTR, _PTR, _PTR, _PTR,
+                                     _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
+                                     _I64P, _I64P, _I64P, _I64P,
+                                     _c.c_int, _c.c_int, _c.c_float, _c.c_int, _PTR]),
+    "fo_lion_update": (_c.c_int, [_PTR, _PTR, _PTR, _c.c_int64, _c.c_int, _c.c_int, _c.c_int,
+                                  _c.c_double, _c.c_double, _c.c_double, _c.c_double, _c.c_int, _PTR]),
+    "fo_lion_multi_tensor_step": (_c.c_int, [_c.POINTER(_PTR), _c.POINTER(_PTR), _c.POINTER(_PTR), _I64P, _c.c_int,
+                                             _c.c_int, _c.c_int, _c.c_int,
+                                             _c.c_double, _c.c_double, _c.c_double, _c.c_double, _c.c_int, _PTR]),
+    "fo_lion_flat_step": (_c.c_int, [_PTR, _PTR, _PTR, _c.c_int64, _c.c_int64, _c.c_int, _c.c_int, _c.c_int,
+                                     _c.c_double, _c.c_double, _c.c_double, _c.c_double, _c.c_int, _PTR]),
+    "fo_lion_clear_cache": (_c.c_int, []),
+    "fo_launch_count": (_c.c_int64, []),
+    "fo_debug_umma_tile": (_c.c_int, [_PTR, _PTR, _PTR, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _PTR]),
+}
+
+
+def load() -> ctypes.CDLL:
+    """Returns the loaded library, building it first if the sources are newer (needs nvcc)."""
+    global _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        if not os.path.exists(LIB_PATH):
+            from . import build as _build
+
+            try:
+                _build.build()
+            except Exception as exc:  # no nvcc, compile error, ...
+                raise RuntimeError(
+                    f"fast_ops_b200: {LIB_PATH} is missing and could not be built ({exc}); "
+                    "run `python -m fast_ops_b200.build` where nvcc is available") from exc
+        lib = ctypes.CDLL(LIB_PATH)
+        for name, (restype, argtypes) in SIGNATURES.items():
+            fn = getattr(lib, name)  # AttributeError here means header and library disagree
+            fn.restype = restype
+            fn.argtypes = argtypes
+        _lib = lib
+        return lib
+
+
+def check(rc: int) -> None:
+    """Turns a non-zero status into RuntimeError carrying the library's message."""
+    if rc != 0:
+        msg = load().fo_last_error().decode("utf-8", "replace")
+        raise RuntimeError(f"fast_ops_b200 error {rc}: {msg}")
+
+
+def dtype_code(dtype) -> int:
+    import torch
+
+    try:
+        return {torch.float16: FO_F16, torch.bfloat16: FO_BF16, torch.float32: FO_F32}[dtype]
+    except KeyError:
+        raise RuntimeError(f"unsupported dtype {dtype}") from None
+
+
+def current_stream_ptr(device) -> int:
+    import torch
+
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def device_status(device_index: int, reset: bool = False) -> int:
+    out = ctypes.c_int(0)
+    check(load().fo_device_status(int(device_index), ctypes.byref(out), int(reset)))
+    return out.value

@@ -1,0 +1,281 @@
+// FlashAttention forward for sm_100a: host launcher behind fo_flash_attn_fwd, the tensor-map
+// (TMA descriptor) construction, and the one-tile self-test of the tensor-core building blocks.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+
+#include "flash_attn_simple.cuh"
+#include "flash_attn_ws.cuh"
+#include "fo_host.h"
+
+namespace {
+
+using fo::AttnParams;
+using fo::kBlockM;
+using fo::kBlockN;
+using fo::kBoxCols;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// cuTensorMapEncodeTiled comes from the driver; resolving it through the runtime avoids
+// linking against libcuda.
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// Tensor map over a (B, H, S, D) tensor with element strides (sb, sh, ss, 1): dimensions are
+// listed innermost first, the box is one [128 rows x 64 columns] swizzled tile, and reads
+// past S are filled with zeros.
+int make_tensor_map(CUtensorMap* map, const void* base, int dtype, int B, int H, int S, int D,
+                    const int64_t strides[3], const char* name) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fo::fail(FO_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  FO_REQUIRE((reinterpret_cast<uintptr_t>(base) & 15) == 0, "%s must be 16-byte aligned", name);
+  // A dimension of extent 1 never uses its stride; give it a harmless one.
+  int64_t sb = B > 1 ? strides[0] : static_cast<int64_t>(H) * S * D;
+  int64_t sh = H > 1 ? strides[1] : static_cast<int64_t>(S) * D;
+  int64_t ss = S > 1 ? strides[2] : D;
+  FO_REQUIRE(sb > 0 && sh > 0 && ss >= D, "%s: strides must be positive and rows must not overlap", name);
+  FO_REQUIRE(sb % 8 == 0 && sh % 8 == 0 && ss % 8 == 0, "%s: strides must be multiples of 8 elements", name);
+  const cuuint64_t dims[4] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(S), static_cast<cuuint64_t>(H),
+                              static_cast<cuuint64_t>(B)};
+  const cuuint64_t gstrides[3] = {static_cast<cuuint64_t>(ss) * 2, static_cast<cuuint64_t>(sh) * 2,
+                                  static_cast<cuuint64_t>(sb) * 2};
+  const cuuint32_t box[4] = {kBoxCols, kBlockN, 1, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUtensorMapDataType dt = dtype == FO_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUresult r = fn(map, dt, 4, const_cast<void*>(base), dims, gstrides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fo::fail(FO_ERR_CUDA, "cuTensorMapEncodeTiled(%s) failed with CUresult %d", name, (int)r);
+  return FO_OK;
+}
+
+// ---- one-tile self-test ------------------------------------------------------------------------
+// mode 0: C = A B^T, A (128 x K) and B (N x K) K-major through TMA (the QK^T path).
+// mode 1: C = A B, A (128 x K) placed in tensor memory by the threads as packed 16-bit pairs,
+//         B (K x N) with N contiguous through TMA (the PV path).
+template <bool kBf16>
+__global__ void __launch_bounds__(128)
+umma_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                 const uint16_t* __restrict__ a_global, float* __restrict__ c, int N, int K, int mode,
+                 int* device_status) {
+  using namespace fo;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint8_t* sA = smem;               // up to 2 boxes
+  uint8_t* sB = smem + 2 * kBoxBytes;  // up to 2 boxes
+  uint64_t* bar_tma = reinterpret_cast<uint64_t*>(smem + 4 * kBoxBytes);
+  uint64_t* bar_mma = bar_tma + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_tma + 2);
+  volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  if (tid == 0) {
+    *cta_abort = 0;
+    mbar_init(bar_tma, 1);
+    mbar_init(bar_mma, 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, 256);
+    tmem_relinquish_alloc_permit();
+  }
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  tcgen05_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+  const uint32_t tC = tmem_base;        // N fp32 columns
+  const uint32_t tA = tmem_base + 128;  // K/2 packed columns (mode 1)
+
+  if (mode == 0) {
+    // A: rows 0..127, K columns -> K/64 boxes; B: rows 0..N-1 (box is 128 rows; rows >= N are
+    // zero-filled), K columns.
+    if (tid == 0) {
+      const int boxes = K / kBoxCols;
+      mbar_arrive_expect_tx(bar_tma, 2 * boxes * kBoxBytes);
+      for (int cb = 0; cb < boxes; ++cb) tma_load_4d(sA + cb * kBoxBytes, &tm_a, bar_tma, cb * kBoxCols, 0, 0, 0);
+      for (int cb = 0; cb < boxes; ++cb) tma_load_4d(sB + cb * kBoxBytes, &tm_b, bar_tma, cb * kBoxCols, 0, 0, 0);
+    }
+    mbar_wait(bar_tma, 0, cta_abort, device_status, FO_STATUS_TIMEOUT_TMA);
+    if (tid == 0) {
+      tcgen05_fence_after_sync();
+      const uint32_t idesc = make_idesc(kBf16, 128, N, 0, 0);
+      for (int kk = 0; kk < K / 16; ++kk)
+        umma_ss(tC, kmajor_desc(smem_u32(sA), kk), kmajor_desc(smem_u32(sB), kk), idesc, kk > 0 ? 1u : 0u);
+      tcgen05_commit(bar_mma);
+    }
+  } else {
+    // B: K rows (box: 128 rows, rows >= K zero-filled), N columns -> N/64 boxes.
+    if (tid == 0) {
+      const int boxes = N / kBoxCols;
+      mbar_arrive_expect_tx(bar_tma, boxes * kBoxBytes);
+      for (int cb = 0; cb < boxes; ++cb) tma_load_4d(sB + cb * kBoxBytes, &tm_b, bar_tma, cb * kBoxCols, 0, 0, 0);
+    }
+    // A: thread t writes row t as packed pairs (element 2c in the low half of column c).
+    const uint32_t* arow = reinterpret_cast<const uint32_t*>(a_global + static_cast<size_t>(tid) * K);
+    for (int cb = 0; cb < K / 2; cb += 32) {
+      uint32_t regs[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) regs[i] = arow[cb + i];
+      tmem_st32(tA + lane_base + cb, regs);
+    }
+    tcgen05_wait_st();
+    tcgen05_fence_before_sync();
+    mbar_wait(bar_tma, 0, cta_abort, device_status, FO_STATUS_TIMEOUT_TMA);
+    __syncthreads();
+    if (tid == 0) {
+      tcgen05_fence_after_sync();
+      const uint32_t idesc = make_idesc(kBf16, 128, N, 0, 1);
+      for (int kk = 0; kk < K / 16; ++kk)
+        umma_ts(tC, tA + kk * 8, nmajor_desc(smem_u32(sB), kk), idesc, kk > 0 ? 1u : 0u);
+      tcgen05_commit(bar_mma);
+    }
+  }
+  mbar_wait(bar_mma, 0, cta_abort, device_status, FO_STATUS_TIMEOUT_MMA);
+  tcgen05_fence_after_sync();
+  for (int cb = 0; cb < N; cb += 32) {
+    uint32_t regs[32];
+    tmem_ld32(tC + lane_base + cb, regs);
+    tcgen05_wait_ld();
+#pragma unroll
+    for (int i = 0; i < 32; ++i) c[static_cast<size_t>(tid) * N + cb + i] = __uint_as_float(regs[i]);
+  }
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem_base, 256);
+}
+
+template <typename Kernel>
+int set_smem(Kernel kernel, int bytes) {
+  FO_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  return FO_OK;
+}
+
+enum class AttnImpl { kSimple, kWarpSpecialized };
+
+// FO_ATTN_IMPL=simple|ws selects the kernel (default: the warp-specialised one).
+AttnImpl chosen_impl() {
+  const char* e = std::getenv("FO_ATTN_IMPL");
+  if (e && std::strcmp(e, "simple") == 0) return AttnImpl::kSimple;
+  return AttnImpl::kWarpSpecialized;
+}
+
+template <int D, bool kBf16>
+int launch_simple(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& prm,
+                  cudaStream_t stream) {
+  auto kernel = fo::attn_fwd_simple_kernel<D, kBf16>;
+  constexpr int smem = fo::simple_smem_bytes<D>();
+  if (int rc = set_smem(kernel, smem)) return rc;
+  dim3 grid(prm.num_q_tiles, prm.B * prm.H);
+  kernel<<<grid, 128, smem, stream>>>(tq, tk, tv, prm);
+  fo::g_launch_count.fetch_add(1, std::memory_order_relaxed);
+  FO_CUDA_CHECK(cudaGetLastError());
+  return FO_OK;
+}
+
+}  // namespace
+
+extern "C" int fo_flash_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
+                                 int B, int H, int Sq, int Sk, int D,
+                                 const int64_t q_strides[3], const int64_t k_strides[3],
+                                 const int64_t v_strides[3], const int64_t o_strides[3],
+                                 int dtype, int causal, float softmax_scale, int device, void* stream) {
+  fo::clear_error();
+  FO_REQUIRE(q && k && v && o, "null tensor pointer");
+  FO_REQUIRE(q_strides && k_strides && v_strides && o_strides, "null stride array");
+  FO_REQUIRE(dtype == FO_F16 || dtype == FO_BF16, "attention inputs must be fp16 or bf16 (got dtype %d)", dtype);
+  FO_REQUIRE(B > 0 && H > 0 && Sq > 0 && Sk > 0, "B, H, Sq, Sk must be positive (got %d %d %d %d)", B, H, Sq, Sk);
+  FO_REQUIRE(static_cast<int64_t>(B) * H <= 65535, "B*H must be <= 65535 (got %lld)", (long long)B * H);
+  if (D != 64 && D != 128) {
+    if (D <= 0 || D > 128 || D % 8 != 0)
+      return fo::fail(FO_ERR_INVALID_ARGUMENT, "head_dim must be a multiple of 8 and <= 128 (got %d)", D);
+    return fo::fail(FO_ERR_UNSUPPORTED, "head_dim %d has no kernel in this build (64 and 128 do)", D);
+  }
+  FO_REQUIRE(softmax_scale > 0.f && std::isfinite(softmax_scale), "softmax_scale must be positive and finite");
+  FO_REQUIRE((reinterpret_cast<uintptr_t>(o) & 15) == 0, "o must be 16-byte aligned");
+  for (int i = 0; i < 3; ++i)
+    FO_REQUIRE(o_strides[i] % 8 == 0 && o_strides[i] >= 0, "o: strides must be non-negative multiples of 8 elements");
+
+  fo::DeviceGuard guard(device);
+  FO_REQUIRE(guard.ok, "cannot make device %d current", device);
+  int* status = fo::device_status_ptr(device);
+  if (!status) return fo::fail(FO_ERR_CUDA, "cannot resolve the status word of device %d", device);
+
+  CUtensorMap tq, tk, tv;
+  if (int rc = make_tensor_map(&tq, q, dtype, B, H, Sq, D, q_strides, "q")) return rc;
+  if (int rc = make_tensor_map(&tk, k, dtype, B, H, Sk, D, k_strides, "k")) return rc;
+  if (int rc = make_tensor_map(&tv, v, dtype, B, H, Sk, D, v_strides, "v")) return rc;
+
+  AttnParams prm;
+  prm.o = o;
+  prm.lse = lse;
+  prm.o_stride_b = o_strides[0];
+  prm.o_stride_h = o_strides[1];
+  prm.o_stride_s = o_strides[2];
+  prm.B = B;
+  prm.H = H;
+  prm.Sq = Sq;
+  prm.Sk = Sk;
+  prm.causal = causal ? 1 : 0;
+  prm.scale_log2 = softmax_scale * 1.4426950408889634f;
+  prm.device_status = status;
+  prm.num_q_tiles = (Sq + kBlockM - 1) / kBlockM;
+
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool bf16 = dtype == FO_BF16;
+  if (chosen_impl() == AttnImpl::kWarpSpecialized) {
+    if (D == 128) return bf16 ? fo::launch_ws<128, true>(tq, tk, tv, prm, s) : fo::launch_ws<128, false>(tq, tk, tv, prm, s);
+    return bf16 ? fo::launch_ws<64, true>(tq, tk, tv, prm, s) : fo::launch_ws<64, false>(tq, tk, tv, prm, s);
+  }
+  if (D == 128) return bf16 ? launch_simple<128, true>(tq, tk, tv, prm, s) : launch_simple<128, false>(tq, tk, tv, prm, s);
+  return bf16 ? launch_simple<64, true>(tq, tk, tv, prm, s) : launch_simple<64, false>(tq, tk, tv, prm, s);
+}
+
+extern "C" int fo_debug_umma_tile(const void* a, const void* b, float* c, int N, int K, int dtype, int mode,
+                                  int device, void* stream) {
+  fo::clear_error();
+  FO_REQUIRE(a && b && c, "null pointer");
+  FO_REQUIRE(dtype == FO_F16 || dtype == FO_BF16, "dtype must be fp16 or bf16");
+  FO_REQUIRE((N == 64 || N == 128) && (K == 64 || K == 128), "N and K must be 64 or 128");
+  FO_REQUIRE(mode == 0 || mode == 1, "mode must be 0 or 1");
+  fo::DeviceGuard guard(device);
+  FO_REQUIRE(guard.ok, "cannot make device %d current", device);
+  int* status = fo::device_status_ptr(device);
+  if (!status) return fo::fail(FO_ERR_CUDA, "cannot resolve the status word of device %d", device);
+  CUtensorMap ta, tb;
+  // A is (128 x K); B is (N x K) in mode 0 and (K x N) in mode 1, both row-major and dense.
+  const int64_t sa[3] = {128LL * K, 128LL * K, K};
+  if (int rc = make_tensor_map(&ta, a, dtype, 1, 1, 128, K, sa, "a")) return rc;
+  const int b_rows = mode == 0 ? N : K, b_cols = mode == 0 ? K : N;
+  const int64_t sb[3] = {static_cast<int64_t>(b_rows) * b_cols, static_cast<int64_t>(b_rows) * b_cols, b_cols};
+  if (int rc = make_tensor_map(&tb, b, dtype, 1, 1, b_rows, b_cols, sb, "b")) return rc;
+  const int smem = 4 * fo::kBoxBytes + 1024 + 128;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == FO_BF16) {
+    if (int rc = set_smem(umma_tile_kernel<true>, smem)) return rc;
+    umma_tile_kernel<true><<<1, 128, smem, s>>>(ta, tb, static_cast<const uint16_t*>(a), c, N, K, mode, status);
+  } else {
+    if (int rc = set_smem(umma_tile_kernel<false>, smem)) return rc;
+    umma_tile_kernel<false><<<1, 128, smem, s>>>(ta, tb, static_cast<const uint16_t*>(a), c, N, K, mode, status);
+  }
+  fo::g_launch_count.fetch_add(1, std::memory_order_relaxed);
+  FO_CUDA_CHECK(cudaGetLastError());
+  return FO_OK;
+}

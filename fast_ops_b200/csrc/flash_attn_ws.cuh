@@ -1,0 +1,401 @@
+// Attention forward, warp-specialised kernel for sm_100a.
+//
+// One CTA owns TWO consecutive 128-row query tiles of one (batch, head) and walks the key/value
+// tiles once for both.  Sixteen warps, four roles:
+//
+//   warps  0-3   softmax of query tile 0      (one thread per row: tcgen05.ld S, max, exp2,
+//   warps  4-7   softmax of query tile 1       pack to 16 bit, tcgen05.st P over S)
+//   warps  8-11  correction: rescales the O accumulators in tensor memory when a row maximum
+//                moved, and at the end divides by the row sum and writes O and LSE
+//   warp   12    MMA issuer: S = Q K^T (operands in shared memory) and O += P V (P from tensor
+//                memory, V from shared memory), accumulators in tensor memory
+//   warp   13    TMA producer: Q once, then K0 V0 K1 V1 ... through a ring of shared-memory stages
+//   warps 14-15  idle (they give their registers to the softmax warps)
+//
+// Tensor memory (512 columns): S0 | S1 | O0 | O1; P_s overwrites the first 64 columns of S_s.
+// While the softmax warps of one tile work on S_j, the tensor core runs the other tile's PV and
+// next QK^T, so MMA and exponentials overlap.  With a causal mask only key tiles at or below
+// the diagonal are visited; tile 1 has one more than tile 0.
+#pragma once
+
+#include "flash_attn_common.cuh"
+#include "fo_host.h"
+
+namespace fo {
+
+template <int D>
+struct WsConfig {
+  static constexpr int kTileBytes = kBlockM * D * 2;
+  static constexpr int kStages = (D == 128) ? 4 : 6;
+  static constexpr int kBoxes = D / kBoxCols;
+  static constexpr int kOffQ = 0;
+  static constexpr int kOffKV = 2 * kTileBytes;
+  static constexpr int kOffAlpha = kOffKV + kStages * kTileBytes;  // [2 tiles][2 buffers][128] float
+  static constexpr int kOffFinal = kOffAlpha + 2 * 2 * 128 * 4;    // [2 tiles][l, m][128] float
+  static constexpr int kOffBars = kOffFinal + 2 * 2 * 128 * 4;
+  static constexpr int kNumBars = 1 + 2 * kStages + 2 * 6;
+  static constexpr int kOffMisc = kOffBars + kNumBars * 8;
+  static constexpr int kSmemBytes = kOffMisc + 64 + 1024 /* alignment slack */;
+  static constexpr uint32_t kTmemCols = 512;
+  static constexpr uint32_t kColS0 = 0, kColO0 = 256;
+};
+
+// A row keeps its reference maximum until the true maximum exceeds it by this much (log2
+// units): exp2 arguments then stay below 8, P stays below 256, and most key tiles need no
+// rescaling of O at all.
+constexpr float kRescaleThreshold = 8.0f;
+
+template <int kRegs> __device__ __forceinline__ void reg_alloc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+template <int kRegs> __device__ __forceinline__ void reg_dealloc() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+
+// grid = (num_q_pairs * B * H); block = 512.  Block w handles pair (num_pairs - 1 - w / (B*H)) of
+// head (w % (B*H)): with a causal mask the pairs with the most key tiles are scheduled first.
+template <int D, bool kBf16>
+__global__ void __launch_bounds__(512, 1)
+attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                   const __grid_constant__ CUtensorMap tm_v, const AttnParams prm) {
+  using Cfg = WsConfig<D>;
+  constexpr int kTileBytes = Cfg::kTileBytes;
+  constexpr int kStages = Cfg::kStages;
+  constexpr int kBoxes = Cfg::kBoxes;
+
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint8_t* sQ = smem + Cfg::kOffQ;    // two tiles
+  uint8_t* sKV = smem + Cfg::kOffKV;  // kStages tiles
+  float* s_alpha = reinterpret_cast<float*>(smem + Cfg::kOffAlpha);
+  float* s_final = reinterpret_cast<float*>(smem + Cfg::kOffFinal);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kOffBars);
+  uint64_t* bar_q_full = bars;                  // TMA -> MMA
+  uint64_t* bar_kv_full = bars + 1;             // [kStages] TMA -> MMA
+  uint64_t* bar_kv_empty = bar_kv_full + kStages;  // [kStages] MMA -> TMA
+  uint64_t* bar_s_full = bar_kv_empty + kStages;   // [2] MMA -> softmax
+  uint64_t* bar_p_full = bar_s_full + 2;           // [2] softmax -> MMA (128 arrivals)
+  uint64_t* bar_o_full = bar_p_full + 2;           // [2] MMA -> correction
+  uint64_t* bar_corr = bar_o_full + 2;             // [2] softmax -> correction (128 arrivals)
+  uint64_t* bar_o_scaled = bar_corr + 2;           // [2] correction -> MMA (128 arrivals)
+  // [2] softmax -> correction, once: final row sum and maximum are in shared memory.  A barrier
+  // of its own, because a fast softmax thread reaches this hand-off while a slower one has not
+  // yet arrived on bar_corr for the last key tile.
+  uint64_t* bar_final = bar_o_scaled + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::kOffMisc);
+  volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* skip = cta_abort + 1;
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int bh_count = prm.B * prm.H;
+  const int num_pairs = (prm.num_q_tiles + 1) >> 1;
+  const int pair = num_pairs - 1 - static_cast<int>(blockIdx.x) / bh_count;
+  const int bh = static_cast<int>(blockIdx.x) % bh_count;
+  const int b = bh / prm.H;
+  const int h = bh - b * prm.H;
+  const int n_kv_total = (prm.Sk + kBlockN - 1) / kBlockN;
+  // key tiles visited by query tile 0 / 1 of this pair; n1 >= n0 >= 1
+  const int n0 = prm.causal ? min(n_kv_total, 2 * pair + 1) : n_kv_total;
+  const int n1 = prm.causal ? min(n_kv_total, 2 * pair + 2) : n_kv_total;
+
+  if (tid == 0) {
+    *cta_abort = 0;
+    *skip = *reinterpret_cast<volatile int*>(prm.device_status);
+    mbar_init(bar_q_full, 1);
+    for (int i = 0; i < kStages; ++i) {
+      mbar_init(bar_kv_full + i, 1);
+      mbar_init(bar_kv_empty + i, 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar_s_full + s, 1);
+      mbar_init(bar_p_full + s, 128);
+      mbar_init(bar_o_full + s, 1);
+      mbar_init(bar_corr + s, 128);
+      mbar_init(bar_o_scaled + s, 128);
+      mbar_init(bar_final + s, 128);
+    }
+    fence_mbar_init();
+    prefetch_tensormap(&tm_q);
+    prefetch_tensormap(&tm_k);
+    prefetch_tensormap(&tm_v);
+  }
+  __syncthreads();
+  if (*skip) return;  // another CTA already timed out: do nothing
+
+  if (warp == 12) {
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish_alloc_permit();
+  }
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  tcgen05_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  int* const dstat = prm.device_status;
+
+  if (warp < 8) {
+    // ================================ softmax ================================
+    reg_alloc<192>();
+    const int s = warp >> 2;
+    const int r = (warp & 3) * 32 + lane;
+    const int q0 = (2 * pair + s) * kBlockM;
+    const int row = q0 + r;
+    const int n_s = s ? n1 : n0;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t tS = tmem_base + Cfg::kColS0 + s * kBlockN + lane_base;
+    float* alpha_slot = s_alpha + s * 256 + r;
+    float m_run = -INFINITY, l_run = 0.f;
+
+    for (int j = 0; j < n_s; ++j) {
+      const int k0 = j * kBlockN;
+      mbar_wait(bar_s_full + s, j & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_MMA);
+      tcgen05_fence_after_sync();
+      uint32_t sr[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, sr[c]);
+      tcgen05_wait_ld();
+
+      const bool need_mask = (k0 + kBlockN > prm.Sk) || (prm.causal && k0 + kBlockN - 1 > q0);
+      float mx = -INFINITY;
+      if (need_mask) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int col = k0 + c * 32 + i;
+            float v = __uint_as_float(sr[c][i]);
+            if (col >= prm.Sk || (prm.causal && col > row)) v = -INFINITY;
+            sr[c][i] = __float_as_uint(v);
+            mx = fmaxf(mx, v);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sr[c][i]));
+        }
+      }
+      const float m_cand = fmaxf(m_run, mx * prm.scale_log2);
+      const float m_new = (m_cand - m_run > kRescaleThreshold) ? m_cand : m_run;
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+      const float alpha = (m_new == m_run) ? 1.f : fast_exp2(m_run - m_use);
+      alpha_slot[(j & 1) * 128] = alpha;
+      mbar_arrive(bar_corr + s);
+
+      float rsum = 0.f;
+      uint32_t pr[2][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c][i]), prm.scale_log2, -m_use));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c][i + 1]), prm.scale_log2, -m_use));
+          rsum += p0 + p1;
+          pr[c >> 1][(c & 1) * 16 + (i >> 1)] = pack2<kBf16>(p0, p1);
+        }
+      }
+      tmem_st32(tS, pr[0]);
+      tmem_st32(tS + 32, pr[1]);
+      tcgen05_wait_st();
+      tcgen05_fence_before_sync();
+      mbar_arrive(bar_p_full + s);
+      l_run = l_run * alpha + rsum;
+      m_run = m_new;
+    }
+    s_final[s * 256 + r] = l_run;
+    s_final[s * 256 + 128 + r] = m_run;
+    mbar_arrive(bar_final + s);
+  } else if (warp < 12) {
+    // ================================ correction + epilogue ================================
+    reg_dealloc<80>();
+    const int r = (warp & 3) * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    for (int j = 0; j < n1; ++j) {
+#pragma unroll
+      for (int s = 0; s < 2; ++s) {
+        if (j >= (s ? n1 : n0)) continue;
+        mbar_wait(bar_corr + s, j & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_SOFTMAX);
+        const float alpha = s_alpha[s * 256 + (j & 1) * 128 + r];
+        if (j > 0) {
+          mbar_wait(bar_o_full + s, (j - 1) & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_MMA);
+          tcgen05_fence_after_sync();
+          if (__any_sync(0xffffffffu, alpha != 1.f)) {
+            const uint32_t tO = tmem_base + Cfg::kColO0 + s * D + lane_base;
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+              uint32_t orr[32];
+              tmem_ld32(tO + c * 32, orr);
+              tcgen05_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
+              tmem_st32(tO + c * 32, orr);
+            }
+            tcgen05_wait_st();
+          }
+          tcgen05_fence_before_sync();
+        }
+        mbar_arrive(bar_o_scaled + s);
+      }
+    }
+    // epilogue: O / l and LSE
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+      const int n_s = s ? n1 : n0;
+      mbar_wait(bar_final + s, 0, cta_abort, dstat, FO_STATUS_TIMEOUT_SOFTMAX);
+      mbar_wait(bar_o_full + s, (n_s - 1) & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_MMA);
+      tcgen05_fence_after_sync();
+      const float l_run = s_final[s * 256 + r];
+      const float m_run = s_final[s * 256 + 128 + r];
+      const float inv_l = (l_run > 0.f) ? 1.f / l_run : 0.f;
+      const int row = (2 * pair + s) * kBlockM + r;
+      const bool row_ok = row < prm.Sq;
+      uint16_t* orow = static_cast<uint16_t*>(prm.o) + b * prm.o_stride_b + h * prm.o_stride_h +
+                       static_cast<int64_t>(row) * prm.o_stride_s;
+      const uint32_t tO = tmem_base + Cfg::kColO0 + s * D + lane_base;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t orr[32];
+        tmem_ld32(tO + c * 32, orr);
+        tcgen05_wait_ld();
+        if (row_ok) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 v;
+            v.x = pack2<kBf16>(__uint_as_float(orr[i + 0]) * inv_l, __uint_as_float(orr[i + 1]) * inv_l);
+            v.y = pack2<kBf16>(__uint_as_float(orr[i + 2]) * inv_l, __uint_as_float(orr[i + 3]) * inv_l);
+            v.z = pack2<kBf16>(__uint_as_float(orr[i + 4]) * inv_l, __uint_as_float(orr[i + 5]) * inv_l);
+            v.w = pack2<kBf16>(__uint_as_float(orr[i + 6]) * inv_l, __uint_as_float(orr[i + 7]) * inv_l);
+            *reinterpret_cast<uint4*>(orow + c * 32 + i) = v;
+          }
+        }
+      }
+      if (row_ok && prm.lse != nullptr) {
+        prm.lse[static_cast<int64_t>(bh) * prm.Sq + row] =
+            (l_run > 0.f) ? (m_run + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
+      }
+    }
+  } else {
+    reg_dealloc<48>();
+    if (warp == 12) {
+      // ================================ MMA issuer ================================
+      constexpr uint32_t idesc_qk = make_idesc(kBf16, kBlockM, kBlockN, 0, 0);
+      constexpr uint32_t idesc_pv = make_idesc(kBf16, kBlockM, D, 0, 1);
+      const uint32_t aQ = smem_u32(sQ);
+      const uint32_t aKV = smem_u32(sKV);
+      const bool issuer = lane == 0;
+
+      auto issue_s = [&](int s, int stage) {
+        const uint32_t tS = tmem_base + Cfg::kColS0 + s * kBlockN;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          umma_ss(tS, kmajor_desc(aQ + s * kTileBytes, kk), kmajor_desc(aKV + stage * kTileBytes, kk), idesc_qk,
+                  kk > 0 ? 1u : 0u);
+      };
+      auto issue_pv = [&](int s, int stage, bool acc) {
+        const uint32_t tP = tmem_base + Cfg::kColS0 + s * kBlockN;
+        const uint32_t tO = tmem_base + Cfg::kColO0 + s * D;
+#pragma unroll
+        for (int kk = 0; kk < kBlockN / 16; ++kk)
+          umma_ts(tO, tP + kk * 8, nmajor_desc(aKV + stage * kTileBytes, kk), idesc_pv, (acc || kk > 0) ? 1u : 0u);
+      };
+
+      mbar_wait(bar_q_full, 0, cta_abort, dstat, FO_STATUS_TIMEOUT_TMA);
+      mbar_wait(bar_kv_full + 0, 0, cta_abort, dstat, FO_STATUS_TIMEOUT_TMA);  // K_0 is ring slot 0
+      tcgen05_fence_after_sync();
+      if (issuer) {
+        issue_s(0, 0);
+        tcgen05_commit(bar_s_full + 0);
+        issue_s(1, 0);
+        tcgen05_commit(bar_s_full + 1);
+        tcgen05_commit(bar_kv_empty + 0);
+      }
+      __syncwarp();
+      for (int j = 0; j < n1; ++j) {
+        const int iv = 2 * j + 1;  // ring index of V_j; K_{j+1} is iv + 1
+        const int st_v = iv % kStages;
+        const int st_k = (iv + 1) % kStages;
+        const bool more = j + 1 < n1;
+        mbar_wait(bar_kv_full + st_v, (iv / kStages) & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_TMA);
+        if (more) mbar_wait(bar_kv_full + st_k, ((iv + 1) / kStages) & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_TMA);
+        if (j < n0) {
+          mbar_wait(bar_p_full + 0, j & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_SOFTMAX);
+          mbar_wait(bar_o_scaled + 0, j & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_SOFTMAX);
+          tcgen05_fence_after_sync();
+          if (issuer) {
+            issue_pv(0, st_v, j > 0);
+            tcgen05_commit(bar_o_full + 0);
+            if (j + 1 < n0) {
+              issue_s(0, st_k);
+              tcgen05_commit(bar_s_full + 0);
+            }
+          }
+          __syncwarp();
+        }
+        mbar_wait(bar_p_full + 1, j & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_SOFTMAX);
+        mbar_wait(bar_o_scaled + 1, j & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_SOFTMAX);
+        tcgen05_fence_after_sync();
+        if (issuer) {
+          issue_pv(1, st_v, j > 0);
+          tcgen05_commit(bar_o_full + 1);
+          tcgen05_commit(bar_kv_empty + st_v);
+          if (more) {
+            issue_s(1, st_k);
+            tcgen05_commit(bar_s_full + 1);
+            tcgen05_commit(bar_kv_empty + st_k);
+          }
+        }
+        __syncwarp();
+      }
+    } else if (warp == 13) {
+      // ================================ TMA producer ================================
+      const bool issuer = lane == 0;
+      if (issuer) {
+        mbar_arrive_expect_tx(bar_q_full, 2 * kTileBytes);
+        for (int s = 0; s < 2; ++s)
+          for (int c = 0; c < kBoxes; ++c)
+            tma_load_4d(sQ + s * kTileBytes + c * kBoxBytes, &tm_q, bar_q_full, c * kBoxCols,
+                        (2 * pair + s) * kBlockM, h, b);
+      }
+      __syncwarp();
+      for (int i = 0; i < 2 * n1; ++i) {
+        const int st = i % kStages;
+        mbar_wait(bar_kv_empty + st, ((i / kStages) & 1) ^ 1, cta_abort, dstat, FO_STATUS_TIMEOUT_MMA);
+        if (issuer) {
+          mbar_arrive_expect_tx(bar_kv_full + st, kTileBytes);
+          const CUtensorMap* map = (i & 1) ? &tm_v : &tm_k;
+          for (int c = 0; c < kBoxes; ++c)
+            tma_load_4d(sKV + st * kTileBytes + c * kBoxBytes, map, bar_kv_full + st, c * kBoxCols,
+                        (i >> 1) * kBlockN, h, b);
+        }
+        __syncwarp();
+      }
+    }
+  }
+
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  if (warp == 12) tmem_dealloc(tmem_base, Cfg::kTmemCols);
+}
+
+template <int D, bool kBf16>
+int launch_ws(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& prm,
+              cudaStream_t stream) {
+  auto kernel = attn_fwd_ws_kernel<D, kBf16>;
+  constexpr int smem = WsConfig<D>::kSmemBytes;
+  // The attribute is per device; setting it again is cheap and keeps multi-device callers right.
+  cudaError_t ea = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (ea != cudaSuccess)
+    return fail(FO_ERR_CUDA, "cudaFuncSetAttribute(shared memory %d) failed: %s", smem, cudaGetErrorString(ea));
+  const int num_pairs = (prm.num_q_tiles + 1) / 2;
+  const int64_t blocks = static_cast<int64_t>(num_pairs) * prm.B * prm.H;
+  if (blocks > 0x7fffffffLL) return fail(FO_ERR_INVALID_ARGUMENT, "too many query tiles for one launch");
+  kernel<<<static_cast<unsigned>(blocks), 512, smem, stream>>>(tq, tk, tv, prm);
+  g_launch_count.fetch_add(1, std::memory_order_relaxed);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(FO_ERR_CUDA, "attention launch failed: %s", cudaGetErrorString(e));
+  return FO_OK;
+}
+
+}  // namespace fo

@@ -1,0 +1,61 @@
+// Host-side helpers shared by the C-ABI translation units: error text, CUDA call
+// checking, the per-device status word and the launch counter.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+
+#include "../../include/fast_ops_b200.h"
+
+namespace fo {
+
+// Stores a printf-style message as this thread's last error and returns `code`.
+int fail(int code, const char* fmt, ...);
+void clear_error();
+
+// Device-global status word (defined once in capi.cu); kernels OR a non-zero code
+// into it when a bounded wait gives up.
+int* device_status_ptr(int device);  // device address of the word; nullptr on failure
+
+extern std::atomic<int64_t> g_launch_count;
+
+// RAII: make `device` current for the scope, restore the previous one afterwards.
+struct DeviceGuard {
+  int prev = -1;
+  bool ok = false;
+  explicit DeviceGuard(int device) {
+    if (cudaGetDevice(&prev) != cudaSuccess) return;
+    if (prev != device && cudaSetDevice(device) != cudaSuccess) return;
+    ok = true;
+    want = device;
+  }
+  ~DeviceGuard() {
+    if (ok && prev != want) cudaSetDevice(prev);
+  }
+  int want = -1;
+};
+
+}  // namespace fo
+
+#define FO_CUDA_CHECK(expr)                                                              \
+  do {                                                                                   \
+    cudaError_t _e = (expr);                                                             \
+    if (_e != cudaSuccess)                                                               \
+      return fo::fail(FO_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), \
+                      __FILE__, __LINE__);                                               \
+  } while (0)
+
+#define FO_REQUIRE(cond, ...)                                        \
+  do {                                                               \
+    if (!(cond)) return fo::fail(FO_ERR_INVALID_ARGUMENT, __VA_ARGS__); \
+  } while (0)
+
+// Status codes written by kernels (bit flags, OR-ed together).
+#define FO_STATUS_TIMEOUT_TMA 0x1    // a wait for a TMA load gave up
+#define FO_STATUS_TIMEOUT_MMA 0x2    // a wait for a tcgen05.commit gave up
+#define FO_STATUS_TIMEOUT_SOFTMAX 0x4  // a wait on a softmax/correction hand-off gave up
+#define FO_STATUS_TIMEOUT_EPILOGUE 0x8

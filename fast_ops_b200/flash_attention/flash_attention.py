@@ -1,0 +1,98 @@
+"""FlashAttention forward with the reference's call signature.
+
+Mirrors fast_ops/flash_attention/flash_attention.py of jfc4050/fast-ops:
+`multi_head_attention(Q, K, V)` (:48-77) and `FlashAttentionFunction` (:28-45) keep their
+names, argument meaning, (B, H, S, D) layout and error behaviour (a constraint violation
+raises).  The keyword-only extras (`causal`, `softmax_scale`, `return_lse`) follow the
+reference's complete forward (flash_attention_triton.py:720-731); the default call is the
+reference call.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Optional, Tuple, Union
+
+import torch
+from torch import Tensor
+from torch.autograd import Function
+
+from .. import _lib
+
+
+def _strides3(t: Tensor):
+    return (ctypes.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
+
+
+def flash_attention_forward(Q: Tensor, K: Tensor, V: Tensor, *, causal: bool = False,
+                            softmax_scale: Optional[float] = None,
+                            return_lse: bool = False) -> Union[Tensor, Tuple[Tensor, Tensor]]:
+    """O = softmax(scale * Q K^T [+ causal mask]) V on the CUDA device holding Q.
+
+    Q: (B, H, M, D); K, V: (B, H, N, D); fp16 or bf16; D in {64, 128}; the last dimension
+    contiguous, the others with strides that are multiples of 8 elements (so (B, S, H, D)
+    tensors viewed as (B, H, S, D) are accepted without a copy).  Returns O (B, H, M, D) in
+    Q's dtype, plus LSE (B, H, M) fp32 when `return_lse`.
+    """
+    if not (isinstance(Q, Tensor) and isinstance(K, Tensor) and isinstance(V, Tensor)):
+        raise RuntimeError("Q, K, V must be tensors")
+    if Q.dim() != 4 or K.dim() != 4 or V.dim() != 4:
+        raise RuntimeError("Q, K, V must be 4-D (B, H, S, D)")
+    if not Q.is_cuda:
+        raise RuntimeError("fast_ops_b200 attention needs CUDA tensors (there is no CPU path)")
+    if K.device != Q.device or V.device != Q.device:
+        raise RuntimeError("Q, K, V must be on the same device")
+    if Q.dtype not in (torch.float16, torch.bfloat16):
+        raise RuntimeError(f"inputs must be float16 or bfloat16, got {Q.dtype}")
+    if K.dtype != Q.dtype or V.dtype != Q.dtype:
+        raise RuntimeError("Q, K, V must have the same dtype")
+    B, H, M, D = Q.shape
+    if K.shape[0] != B or K.shape[1] != H or K.shape[3] != D or V.shape != K.shape:
+        raise RuntimeError(f"shape mismatch: Q {tuple(Q.shape)}, K {tuple(K.shape)}, V {tuple(V.shape)}")
+    N = K.shape[2]
+    if D > 128 or D % 8 != 0:
+        raise RuntimeError(f"head_dim must be a multiple of 8 and <= 128, got {D}")
+    for name, t in (("Q", Q), ("K", K), ("V", V)):
+        if t.stride(3) != 1:
+            raise RuntimeError(f"{name}: the last dimension must be contiguous")
+    scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(D)
+
+    O = torch.empty((B, H, M, D), dtype=Q.dtype, device=Q.device)
+    lse = torch.empty((B, H, M), dtype=torch.float32, device=Q.device) if return_lse else None
+    lib = _lib.load()
+    rc = lib.fo_flash_attn_fwd(
+        Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(), lse.data_ptr() if return_lse else None,
+        B, H, M, N, D, _strides3(Q), _strides3(K), _strides3(V), _strides3(O),
+        _lib.dtype_code(Q.dtype), int(bool(causal)), scale, Q.device.index,
+        _lib.current_stream_ptr(Q.device))
+    _lib.check(rc)
+    return (O, lse) if return_lse else O
+
+
+class FlashAttentionFunction(Function):
+    """fast_ops/flash_attention/flash_attention.py:28-45: forward only; backward raises."""
+
+    @staticmethod
+    def forward(ctx, Q: Tensor, K: Tensor, V: Tensor) -> Tensor:
+        return flash_attention_forward(Q, K, V)
+
+    @staticmethod
+    def backward(ctx, dO: Tensor):
+        raise NotImplementedError
+
+
+def multi_head_attention(Q: Tensor, K: Tensor, V: Tensor, *, causal: bool = False,
+                         softmax_scale: Optional[float] = None,
+                         return_lse: bool = False) -> Union[Tensor, Tuple[Tensor, Tensor]]:
+    """Drop-in for fast_ops.flash_attention.flash_attention.multi_head_attention (:48-77).
+
+    :param Q: (B, H, M, D) query.  :param K: (B, H, N, D) key.  :param V: (B, H, N, D) value.
+    :returns: (B, H, M, D), or (O, LSE) when `return_lse`.
+
+    Limitations (violations raise RuntimeError): head_dim 64 or 128 in this build (the
+    reference states <= 128 and a multiple of 8); fp16 / bf16 inputs; last dimension
+    contiguous.  The scale is 1/sqrt(D) unless `softmax_scale` is given.
+    """
+    if not causal and softmax_scale is None and not return_lse:
+        return FlashAttentionFunction.apply(Q, K, V)
+    return flash_attention_forward(Q, K, V, causal=causal, softmax_scale=softmax_scale, return_lse=return_lse)

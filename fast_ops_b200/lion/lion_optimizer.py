@@ -1,0 +1,220 @@
+"""Fused Lion optimizer with the reference's torch.optim interface.
+
+Mirrors fast_ops/lion/lion_optimizer.py of jfc4050/fast-ops (`Lion.__init__` :34-55, `step`
+:57-76): same constructor defaults, `RuntimeError` on a non-positive learning rate or a beta
+outside [0, 1], state key "exp_avg", param-group keys lr / betas / weight_decay.  Instead of
+one kernel launch per tensor, `step()` hands every (param, grad, exp_avg) triple of a group to
+ONE multi-tensor kernel launch per dtype combination.  The arithmetic follows the reference
+torch implementation (fast_ops/lion/lion_optimizer_ref.py:51-67) rounding for rounding.
+
+Keyword-only extensions:
+  momentum_dtype   dtype of exp_avg (default: the parameter's dtype, as the reference does at
+                   :68-74; the Lion paper keeps momentum in bf16).
+  process_group    a torch.distributed group: parameters are laid out in one flat buffer, each
+                   rank updates only its 1/world_size slice (and keeps momentum only for it),
+                   then ONE all-gather distributes the updated weights (ZeRO-1).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Dict, Iterable, List, Optional, Tuple
+
+import torch
+from torch import Tensor
+from torch.optim.optimizer import Optimizer
+
+from .. import _lib
+from .zero1 import FlatLayout
+
+
+def lion_update(param: Tensor, grad: Tensor, exp_avg: Tensor, lr: float, beta1: float, beta2: float,
+                weight_decay: float) -> None:
+    """Single-tensor fused step; the signature of the reference extension's `lion_update`
+    (fast_ops/lion/lion.cpp:4-15).  Same checks as its host launcher
+    (fast_ops/lion/lion_update.cu:132-139): param/grad dtypes equal, all three dense."""
+    _check_triple(param, grad, exp_avg)
+    lib = _lib.load()
+    _lib.check(lib.fo_lion_update(
+        param.data_ptr(), grad.data_ptr(), exp_avg.data_ptr(), param.numel(),
+        _lib.dtype_code(param.dtype), _lib.dtype_code(grad.dtype), _lib.dtype_code(exp_avg.dtype),
+        float(lr), float(beta1), float(beta2), float(weight_decay), param.device.index,
+        _lib.current_stream_ptr(param.device)))
+
+
+def _check_triple(param: Tensor, grad: Tensor, exp_avg: Tensor) -> None:
+    if not param.is_cuda:
+        raise RuntimeError("fast_ops_b200 Lion needs CUDA tensors (there is no CPU path)")
+    if grad.device != param.device or exp_avg.device != param.device:
+        raise RuntimeError("param, grad and exp_avg must be on the same device")
+    if param.dtype != grad.dtype:
+        raise RuntimeError(f"param and grad dtypes differ: {param.dtype} vs {grad.dtype}")
+    if grad.shape != param.shape or exp_avg.numel() != param.numel():
+        raise RuntimeError("param, grad and exp_avg must have the same number of elements")
+    for t in (param, grad, exp_avg):
+        if not t.is_non_overlapping_and_dense():
+            raise RuntimeError("expected tensor to be contiguous")
+    if param.stride() != grad.stride():
+        raise RuntimeError("param and grad must share a memory layout")
+
+
+def _flat_step(p: Tensor, g: Tensor, m_shard: Tensor, begin: int, end: int, lr: float, betas, wd: float) -> None:
+    """Lion step on elements [begin, end) of the flat buffers (C-ABI fo_lion_flat_step)."""
+    lib = _lib.load()
+    _lib.check(lib.fo_lion_flat_step(
+        p.data_ptr(), g.data_ptr(), m_shard.data_ptr(), begin, end,
+        _lib.dtype_code(p.dtype), _lib.dtype_code(g.dtype), _lib.dtype_code(m_shard.dtype),
+        float(lr), float(betas[0]), float(betas[1]), float(wd), p.device.index,
+        _lib.current_stream_ptr(p.device)))
+
+
+class _TensorList:
+    """ctypes image of one multi-tensor call, reused while the pointers stay the same."""
+
+    def __init__(self, key, params: List[Tensor], grads: List[Tensor], moms: List[Tensor]):
+        n = len(params)
+        self.key = key
+        self.n = n
+        self.params = (ctypes.c_void_p * n)(*[t.data_ptr() for t in params])
+        self.grads = (ctypes.c_void_p * n)(*[t.data_ptr() for t in grads])
+        self.moms = (ctypes.c_void_p * n)(*[t.data_ptr() for t in moms])
+        self.numels = (ctypes.c_int64 * n)(*[t.numel() for t in params])
+
+
+class Lion(Optimizer):
+    """Lion ("Symbolic Discovery of Optimization Algorithms", arXiv:2302.06675), fused."""
+
+    def __init__(self, params: Iterable, lr: float = 1e-4, betas: Tuple[float, float] = (0.9, 0.99),
+                 weight_decay: float = 0.0, *, momentum_dtype: Optional[torch.dtype] = None,
+                 process_group=None) -> None:
+        if lr <= 0:
+            raise RuntimeError(f"expected positive LR, got {lr}")
+        if not all(0 <= beta <= 1 for beta in betas):
+            raise RuntimeError(f"betas must be between 0 and 1. got {betas}")
+        if momentum_dtype not in (None, torch.float16, torch.bfloat16, torch.float32):
+            raise RuntimeError(f"unsupported momentum dtype {momentum_dtype}")
+        defaults = {"lr": lr, "betas": betas, "weight_decay": weight_decay}
+        super().__init__(params, defaults)
+        self._momentum_dtype = momentum_dtype
+        self._lists: Dict[tuple, _TensorList] = {}
+        self._pg = process_group
+        self._zero = None
+        if process_group is not None:
+            self._zero = _Zero1State(self, process_group, momentum_dtype)
+
+    # -- multi-tensor path ---------------------------------------------------------------
+    @torch.no_grad()
+    def step(self) -> None:
+        """Parameter and momentum update (no closure, no return value: lion_optimizer.py:57)."""
+        if self._zero is not None:
+            self._zero.step()
+            return
+        lib = _lib.load()
+        for gi, group in enumerate(self.param_groups):
+            lr = group["lr"]
+            weight_decay = group["weight_decay"]
+            beta1, beta2 = group["betas"]
+            buckets: Dict[tuple, Tuple[List[Tensor], List[Tensor], List[Tensor]]] = {}
+            for param in group["params"]:
+                grad = param.grad
+                if grad is None:
+                    continue
+                state = self.state[param]
+                if "exp_avg" not in state:
+                    state["exp_avg"] = torch.zeros_like(
+                        param, dtype=self._momentum_dtype or param.dtype, memory_format=torch.preserve_format)
+                exp_avg = state["exp_avg"]
+                _check_triple(param, grad, exp_avg)
+                key = (gi, param.device.index, param.dtype, exp_avg.dtype)
+                ps, gs, ms = buckets.setdefault(key, ([], [], []))
+                ps.append(param)
+                gs.append(grad)
+                ms.append(exp_avg)
+            for key, (ps, gs, ms) in buckets.items():
+                ptr_key = tuple(t.data_ptr() for t in ps) + tuple(t.data_ptr() for t in gs) + tuple(
+                    t.data_ptr() for t in ms)
+                tl = self._lists.get(key)
+                if tl is None or tl.key != ptr_key:
+                    tl = _TensorList(ptr_key, ps, gs, ms)
+                    self._lists[key] = tl
+                device_index = key[1]
+                _lib.check(lib.fo_lion_multi_tensor_step(
+                    tl.params, tl.grads, tl.moms, tl.numels, tl.n,
+                    _lib.dtype_code(key[2]), _lib.dtype_code(key[2]), _lib.dtype_code(key[3]),
+                    float(lr), float(beta1), float(beta2), float(weight_decay), device_index,
+                    _lib.current_stream_ptr(torch.device("cuda", device_index))))
+
+    # -- ZeRO-1 accessors ------------------------------------------------------------------
+    @property
+    def flat_params(self) -> Optional[Tensor]:
+        return None if self._zero is None else self._zero.flat_p
+
+    @property
+    def flat_grads(self) -> Optional[Tensor]:
+        return None if self._zero is None else self._zero.flat_g
+
+
+class _Zero1State:
+    """Flat parameter / gradient buffers, this rank's momentum shard and the step that uses them.
+
+    Every parameter becomes a view into `flat_p`; `p.grad` is pre-set to a view into `flat_g`
+    so that backward accumulates straight into it (a caller that assigns other gradient
+    tensors pays one copy per tensor in step()).  Gradient averaging across ranks is the
+    caller's job (reduce-scatter or all-reduce before step()); the optimizer's one collective is
+    the all-gather of updated weights.
+    """
+
+    def __init__(self, opt: Lion, group, momentum_dtype: Optional[torch.dtype]):
+        import torch.distributed as dist
+
+        self.opt = opt
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        params = [p for g in opt.param_groups for p in g["params"]]
+        if not params:
+            raise RuntimeError("no parameters")
+        if len(opt.param_groups) != 1:
+            raise RuntimeError("process_group mode supports a single param group")
+        dtype, device = params[0].dtype, params[0].device
+        for p in params:
+            if p.dtype != dtype or p.device != device:
+                raise RuntimeError("process_group mode needs all parameters on one device with one dtype")
+        self.params = params
+        self.layout = FlatLayout.build([p.numel() for p in params], self.world)
+        self.flat_p = torch.zeros(self.layout.total, dtype=dtype, device=device)
+        self.flat_g = torch.zeros(self.layout.total, dtype=dtype, device=device)
+        self._grad_views: List[Tensor] = []
+        with torch.no_grad():
+            for p, off in zip(params, self.layout.offsets):
+                n = p.numel()
+                view = self.flat_p[off:off + n].view(p.shape)
+                view.copy_(p.data.contiguous())
+                p.data = view
+                gview = self.flat_g[off:off + n].view(p.shape)
+                if p.grad is not None:
+                    gview.copy_(p.grad)
+                p.grad = gview
+                self._grad_views.append(gview)
+        self.begin, self.end = self.layout.shard_range(self.rank)
+        self.m_shard = torch.zeros(self.end - self.begin, dtype=momentum_dtype or dtype, device=device)
+        for i, p in enumerate(params):
+            _, s0, n = self.layout.tensor_slice_in_shard(i, self.rank)
+            opt.state[p]["exp_avg"] = self.m_shard[s0:s0 + n]
+        self.flat_step_fn = _flat_step
+        self.last_step_ms = None
+
+    @torch.no_grad()
+    def step(self) -> None:
+        import torch.distributed as dist
+
+        for p, gview in zip(self.params, self._grad_views):
+            if p.grad is None:
+                raise RuntimeError("process_group mode needs a gradient for every parameter")
+            if p.grad.data_ptr() != gview.data_ptr():
+                gview.copy_(p.grad)
+                p.grad = gview
+        group = self.opt.param_groups[0]
+        self.flat_step_fn(self.flat_p, self.flat_g, self.m_shard, self.begin, self.end, group["lr"],
+                          group["betas"], group["weight_decay"])
+        if self.world > 1:
+            dist.all_gather_into_tensor(self.flat_p, self.flat_p[self.begin:self.end], group=self.group)

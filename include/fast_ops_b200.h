@@ -1,0 +1,143 @@
+/*
+ * fast_ops_b200 — C ABI of the two B200 (sm_100a) hot paths.
+ *
+ * Every entry point takes plain pointers and sizes; no torch type crosses this
+ * boundary.  All device pointers must belong to `device`.  All launches are
+ * asynchronous on `stream` (a cudaStream_t passed as void*; NULL = the legacy
+ * default stream).  Functions return FO_OK (0) or a negative FO_ERR_* code; the
+ * text of the most recent error on the calling thread is fo_last_error().
+ *
+ * Reference interfaces are cited by their path inside jfc4050/fast-ops.
+ */
+#ifndef FAST_OPS_B200_H
+#define FAST_OPS_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FO_OK 0
+#define FO_ERR_INVALID_ARGUMENT (-1) /* shape / dtype / stride / alignment contract violated */
+#define FO_ERR_CUDA (-2)             /* a CUDA runtime or driver call failed */
+#define FO_ERR_UNSUPPORTED (-3)      /* valid request this build has no kernel for */
+#define FO_ERR_DEVICE_STATUS (-4)    /* a kernel recorded a bounded-wait timeout */
+
+/* Element types.  FO_F32 is accepted only by the Lion entry points. */
+#define FO_F16 0
+#define FO_BF16 1
+#define FO_F32 2
+
+/* Library version: major*10000 + minor*100 + patch. */
+int fo_version(void);
+
+/* Message of the last error returned on this host thread ("" if none). */
+const char* fo_last_error(void);
+
+/*
+ * Device-side status word of `device`: 0 when every kernel launched by this
+ * library so far finished its bounded waits, otherwise a code naming the wait
+ * that gave up (the kernel still ran to its end and freed its tensor memory).
+ * Synchronises the device.  If `reset` is non-zero the word is cleared.
+ */
+int fo_device_status(int device, int* status_out, int reset);
+
+/*
+ * FlashAttention forward:  O = softmax(scale * Q K^T + causal_mask) V,
+ * LSE[b,h,i] = log(sum_j exp(scale * q_i . k_j))  (natural log, fp32).
+ *
+ * Replaces flash_attn_fwd_cuda(Q, K, V) (fast_ops/flash_attention/
+ * flash_attention_fwd.cu:154-181), bound to Python as `forward`
+ * (fast_ops/flash_attention/flash_attention.cpp:12-14).  The reference takes
+ * (B,H,M,D)/(B,H,N,D) tensors and implies scale = 1/sqrt(D); the causal flag
+ * and the LSE output follow the semantics of the reference's complete forward
+ * (fast_ops/flash_attention/flash_attention_triton.py:149-150, :174-175, :255).
+ *
+ *   q, k, v, o : device pointers, fp16 or bf16 (`dtype`), 16-byte aligned.
+ *   lse        : device pointer to B*H*Sq floats (contiguous), or NULL.
+ *   *_strides  : element strides of the batch, head and sequence dimensions
+ *                (in that order); the head_dim stride is 1.  Each stride must
+ *                be a multiple of 8 elements (16 bytes).
+ *   D          : 64 or 128.
+ *   causal     : non-zero masks column j > row i (top-left aligned).
+ *   softmax_scale : multiplies Q K^T; pass 1/sqrt(D) for the reference default.
+ */
+int fo_flash_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
+                      int B, int H, int Sq, int Sk, int D,
+                      const int64_t q_strides[3], const int64_t k_strides[3],
+                      const int64_t v_strides[3], const int64_t o_strides[3],
+                      int dtype, int causal, float softmax_scale,
+                      int device, void* stream);
+
+/*
+ * Fused Lion step on one dense tensor, in place:
+ *   p <- p * (1 - lr*wd);  u = sign(beta1*m + (1-beta1)*g);  p <- p - lr*u;
+ *   m <- beta2*m + (1-beta2)*g
+ * with a rounding to the storage type after every product and sum, which is
+ * what the reference torch implementation does
+ * (fast_ops/lion/lion_optimizer_ref.py:51-67); sign(0) is 0.
+ *
+ * Replaces lion_update(param, grad, exp_avg, lr, beta1, beta2, weight_decay)
+ * (fast_ops/lion/lion_update.cu:121-161, bound at fast_ops/lion/lion.cpp:13-15).
+ * Hyper-parameters are doubles so that the derived constants (1 - lr*wd, ...)
+ * are formed in double and rounded to float once, as torch does with Python
+ * scalars.  p_dtype must equal g_dtype (lion_update.cu:132-133).
+ */
+int fo_lion_update(void* param, const void* grad, void* exp_avg, int64_t numel,
+                   int p_dtype, int g_dtype, int m_dtype,
+                   double lr, double beta1, double beta2, double weight_decay,
+                   int device, void* stream);
+
+/*
+ * The same step over a list of tensors in ONE kernel launch.  Replaces the
+ * per-tensor loop of Lion.step() (fast_ops/lion/lion_optimizer.py:57-76).
+ * `params`, `grads`, `exp_avgs` and `numels` are HOST arrays of n_tensors
+ * entries holding device pointers / element counts.  The device-side tensor
+ * table is built on the first call for a given list and cached inside the
+ * library (keyed by the list's contents), so later calls with the same list
+ * do no host-to-device copy.
+ */
+int fo_lion_multi_tensor_step(void* const* params, const void* const* grads,
+                              void* const* exp_avgs, const int64_t* numels, int n_tensors,
+                              int p_dtype, int g_dtype, int m_dtype,
+                              double lr, double beta1, double beta2, double weight_decay,
+                              int device, void* stream);
+
+/*
+ * The same step on elements [begin, end) of flat buffers: the shard a rank owns
+ * when parameters are partitioned ZeRO-1 style.  `exp_avg` points at the
+ * momentum of element `begin` (a rank keeps momentum for its shard only);
+ * `param` and `grad` point at element 0 of the flat buffers.  No counterpart in
+ * the reference, whose step is per tensor (fast_ops/lion/lion_optimizer.py:64-76).
+ */
+int fo_lion_flat_step(void* param, const void* grad, void* exp_avg_shard,
+                      int64_t begin, int64_t end,
+                      int p_dtype, int g_dtype, int m_dtype,
+                      double lr, double beta1, double beta2, double weight_decay,
+                      int device, void* stream);
+
+/* Drops the cached tensor tables of fo_lion_multi_tensor_step (all devices). */
+int fo_lion_clear_cache(void);
+
+/*
+ * Number of kernels this library has launched since load (all entry points,
+ * this process).  Lets a caller count launches inside a timed region.
+ */
+int64_t fo_launch_count(void);
+
+/*
+ * Self-test hooks for the tensor-core building blocks of the attention kernel
+ * (one 128 x N x K tile through TMA + tcgen05.mma + tcgen05.ld).  mode 0:
+ * C = A B^T with A (128 x K) and B (N x K) both K-major from shared memory;
+ * mode 1: C = A B with A (128 x K) written to tensor memory by the threads and
+ * B (K x N) N-major from shared memory.  a, b: device bf16/fp16; c: device
+ * fp32 128 x N row-major.  K in {64,128}, N in {64,128}.  Test use only.
+ */
+int fo_debug_umma_tile(const void* a, const void* b, float* c, int N, int K,
+                       int dtype, int mode, int device, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FAST_OPS_B200_H */

@@ -1,0 +1,256 @@
+/*
+ * CPU oracle for the two hot paths.  TEST INFRASTRUCTURE ONLY: tests/, the smoke check and
+ * the CPU-baseline leg of bench.py use it as the checker and as the timed CPU reference;
+ * nothing in the product (fast_ops_b200/) may call it.
+ *
+ * It restates, in plain C, what the reference's torch implementations compute:
+ *   - oracle_attention_fwd follows fast_ops/flash_attention/attention_ref.py:41-73
+ *     (upcast to fp32, scores = (q/sqrt(d)) . k, causal triu(.,1) -> -inf, softmax, P V);
+ *     the LSE it also returns is the quantity the reference's complete forward stores
+ *     (fast_ops/flash_attention/flash_attention_triton.py:241-255).
+ *   - oracle_lion_step follows fast_ops/lion/lion_optimizer_ref.py:51-67, including the
+ *     rounding to the storage type after each tensor op and torch's handling of scalars
+ *     (a `mul` scalar stays fp32; an `add_(..., alpha=a)` rounds a to the promoted tensor
+ *     type and evaluates self + a*other as one fused multiply-add in fp32).
+ *
+ * Parity is pinned: tests/test_oracle_golden.py checks both functions against vectors
+ * produced by importing the reference itself (tests/golden/make_golden.py).
+ */
+#include <math.h>
+#include <pthread.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+#include <unistd.h>
+
+#define ORACLE_F16 0
+#define ORACLE_BF16 1
+#define ORACLE_F32 2
+
+/* ---- a small parallel-for on pthreads (this image's gcc ships no OpenMP runtime) -------- */
+
+static int g_threads = 0; /* 0 = one per online core */
+
+int oracle_num_threads(void) {
+  if (g_threads > 0) return g_threads;
+  long n = sysconf(_SC_NPROCESSORS_ONLN);
+  return n > 0 ? (int)n : 1;
+}
+
+void oracle_set_num_threads(int n) { g_threads = n > 0 ? n : 0; }
+
+typedef void (*range_fn)(int64_t begin, int64_t end, void* ctx);
+
+typedef struct {
+  range_fn fn;
+  void* ctx;
+  int64_t total, grain;
+  int64_t next; /* next unclaimed index, advanced atomically */
+} par_job;
+
+static void* par_worker(void* arg) {
+  par_job* job = (par_job*)arg;
+  for (;;) {
+    const int64_t b = __atomic_fetch_add(&job->next, job->grain, __ATOMIC_RELAXED);
+    if (b >= job->total) break;
+    const int64_t e = b + job->grain < job->total ? b + job->grain : job->total;
+    job->fn(b, e, job->ctx);
+  }
+  return NULL;
+}
+
+/* Runs fn over [0, total) in pieces of `grain`, handed out dynamically to the threads. */
+static void parallel_for(int64_t total, int64_t grain, range_fn fn, void* ctx) {
+  if (total <= 0) return;
+  int nt = oracle_num_threads();
+  if ((int64_t)nt * grain > total) nt = (int)((total + grain - 1) / grain);
+  par_job job = {fn, ctx, total, grain, 0};
+  if (nt <= 1) {
+    par_worker(&job);
+    return;
+  }
+  pthread_t* th = (pthread_t*)malloc(sizeof(pthread_t) * (size_t)nt);
+  int started = 0;
+  for (int i = 0; i < nt - 1; ++i) {
+    if (pthread_create(&th[started], NULL, par_worker, &job) == 0) ++started;
+  }
+  par_worker(&job);
+  for (int i = 0; i < started; ++i) pthread_join(th[i], NULL);
+  free(th);
+}
+
+/* ---- storage-type conversions (round to nearest even) ---------------------------------- */
+
+static inline float bf16_to_f32(uint16_t h) {
+  uint32_t u = ((uint32_t)h) << 16;
+  float f;
+  memcpy(&f, &u, 4);
+  return f;
+}
+
+static inline uint16_t f32_to_bf16(float f) {
+  uint32_t u;
+  memcpy(&u, &f, 4);
+  if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x0040u); /* quiet NaN */
+  uint32_t lsb = (u >> 16) & 1u;
+  u += 0x7fffu + lsb;
+  return (uint16_t)(u >> 16);
+}
+
+static inline float f16_to_f32(uint16_t h) {
+  _Float16 x;
+  memcpy(&x, &h, 2);
+  return (float)x;
+}
+
+static inline uint16_t f32_to_f16(float f) {
+  _Float16 x = (_Float16)f; /* IEEE round-to-nearest-even */
+  uint16_t h;
+  memcpy(&h, &x, 2);
+  return h;
+}
+
+static inline float round_to(float x, int dtype) {
+  if (dtype == ORACLE_BF16) return bf16_to_f32(f32_to_bf16(x));
+  if (dtype == ORACLE_F16) return f16_to_f32(f32_to_f16(x));
+  return x;
+}
+
+static inline float load_elem(const void* base, int64_t i, int dtype) {
+  if (dtype == ORACLE_F32) return ((const float*)base)[i];
+  uint16_t h = ((const uint16_t*)base)[i];
+  return dtype == ORACLE_BF16 ? bf16_to_f32(h) : f16_to_f32(h);
+}
+
+static inline void store_elem(void* base, int64_t i, int dtype, float x) {
+  if (dtype == ORACLE_F32) ((float*)base)[i] = x;
+  else if (dtype == ORACLE_BF16) ((uint16_t*)base)[i] = f32_to_bf16(x);
+  else ((uint16_t*)base)[i] = f32_to_f16(x);
+}
+
+static inline int promote(int a, int b) { return a == b ? a : ORACLE_F32; }
+
+/* ---- Lion -------------------------------------------------------------------------------
+ * One step on one tensor, in place.  param/grad share p_dtype (the reference's fused kernel
+ * requires it, fast_ops/lion/lion_update.cu:132-133); exp_avg has m_dtype.
+ * Lines cited are of fast_ops/lion/lion_optimizer_ref.py. */
+typedef struct {
+  void* param;
+  const void* grad;
+  void* exp_avg;
+  int p_dtype, m_dtype;
+  double lr, beta1, beta2, weight_decay;
+} lion_ctx;
+
+static void lion_range(int64_t begin, int64_t end, void* vctx) {
+  const lion_ctx* c = (const lion_ctx*)vctx;
+  void* param = c->param;
+  const void* grad = c->grad;
+  void* exp_avg = c->exp_avg;
+  const int p_dtype = c->p_dtype, m_dtype = c->m_dtype;
+  const int u_dtype = promote(p_dtype, m_dtype);
+  const float c_wd = (float)(1.0 - c->lr * c->weight_decay);
+  const float c_b1 = (float)c->beta1;
+  const float c_1mb1 = (float)(1.0 - c->beta1);
+  const float c_b2 = (float)c->beta2;
+  const float c_nlr = round_to((float)(-c->lr), u_dtype);
+  const float c_1mb2 = round_to((float)(1.0 - c->beta2), u_dtype);
+  for (int64_t i = begin; i < end; ++i) {
+    const float p = load_elem(param, i, p_dtype);
+    const float g = load_elem(grad, i, p_dtype);
+    const float m = load_elem(exp_avg, i, m_dtype);
+    /* :51  p.data.mul_(1 - lr * wd) */
+    const float p1 = round_to(p * c_wd, p_dtype);
+    /* :64  update = exp_avg * beta1 + grad * (1 - beta1)   (three ops, each rounded) */
+    const float t1 = round_to(m * c_b1, m_dtype);
+    const float t2 = round_to(g * c_1mb1, p_dtype);
+    const float u = round_to(t1 + t2, u_dtype);
+    const float s = (u > 0.f) ? 1.f : ((u < 0.f) ? -1.f : 0.f);
+    /* :65  p.add_(torch.sign(update), alpha=-lr) */
+    store_elem(param, i, p_dtype, fmaf(c_nlr, s, p1));
+    /* :67  exp_avg.mul_(beta2).add_(grad, alpha=1 - beta2) */
+    const float m1 = round_to(m * c_b2, m_dtype);
+    store_elem(exp_avg, i, m_dtype, fmaf(c_1mb2, g, m1));
+  }
+}
+
+void oracle_lion_step(void* param, const void* grad, void* exp_avg, int64_t numel, int p_dtype,
+                      int m_dtype, double lr, double beta1, double beta2, double weight_decay) {
+  lion_ctx ctx = {param, grad, exp_avg, p_dtype, m_dtype, lr, beta1, beta2, weight_decay};
+  parallel_for(numel, 1 << 16, lion_range, &ctx);
+}
+
+/* ---- attention --------------------------------------------------------------------------
+ * q: (B,H,Sq,D), k/v: (B,H,Sk,D), all fp32 and dense; out: (B,H,Sq,D) fp32; lse: (B,H,Sq)
+ * fp32 or NULL.  `scale` multiplies q before the dot products (attention_ref.py:46 divides q
+ * by sqrt(d); pass 1/sqrt(d)).  Causal masking is top-left aligned: column j > row i is
+ * -inf (attention_ref.py:54-58).  `bh_begin/bh_end` restrict the work to a range of flattened
+ * (batch, head) pairs so that a bounded sample of a large problem can be timed. */
+typedef struct {
+  const float *q, *k, *v;
+  float *out, *lse;
+  int Sq, Sk, D, causal, bh_begin;
+  float scale;
+} attn_ctx;
+
+static void attn_range(int64_t begin, int64_t end, void* vctx) {
+  const attn_ctx* c = (const attn_ctx*)vctx;
+  const float *q = c->q, *k = c->k, *v = c->v;
+  float *out = c->out, *lse = c->lse;
+  const int Sq = c->Sq, Sk = c->Sk, D = c->D, causal = c->causal, bh_begin = c->bh_begin;
+  const float scale = c->scale;
+  {
+    float* scores = (float*)malloc(sizeof(float) * (size_t)(Sk > 0 ? Sk : 1));
+    float* qs = (float*)malloc(sizeof(float) * (size_t)D);
+    float* acc = (float*)malloc(sizeof(float) * (size_t)D);
+    for (int64_t r = begin; r < end; ++r) {
+      const int bh = bh_begin + (int)(r / Sq);
+      const int i = (int)(r % Sq);
+      const float* qi = q + ((int64_t)bh * Sq + i) * D;
+      const float* kb = k + (int64_t)bh * Sk * D;
+      const float* vb = v + (int64_t)bh * Sk * D;
+      float* oi = out + ((int64_t)bh * Sq + i) * D;
+      int n = Sk;
+      if (causal && i + 1 < n) n = i + 1;
+      for (int d = 0; d < D; ++d) qs[d] = qi[d] * scale;
+      float mx = -INFINITY;
+      for (int j = 0; j < n; ++j) {
+        const float* kj = kb + (int64_t)j * D;
+        float s = 0.f;
+#pragma omp simd reduction(+ : s)
+        for (int d = 0; d < D; ++d) s += qs[d] * kj[d];
+        scores[j] = s;
+        if (s > mx) mx = s;
+      }
+      float sum = 0.f;
+      for (int j = 0; j < n; ++j) {
+        const float e = expf(scores[j] - mx);
+        scores[j] = e;
+        sum += e;
+      }
+      for (int d = 0; d < D; ++d) acc[d] = 0.f;
+      for (int j = 0; j < n; ++j) {
+        const float pj = scores[j];
+        const float* vj = vb + (int64_t)j * D;
+#pragma omp simd
+        for (int d = 0; d < D; ++d) acc[d] += pj * vj[d];
+      }
+      const float inv = 1.f / sum;
+      for (int d = 0; d < D; ++d) oi[d] = acc[d] * inv;
+      if (lse) lse[(int64_t)bh * Sq + i] = mx + logf(sum);
+    }
+    free(scores);
+    free(qs);
+    free(acc);
+  }
+}
+
+void oracle_attention_fwd(const float* q, const float* k, const float* v, float* out, float* lse,
+                          int B, int H, int Sq, int Sk, int D, int causal, float scale,
+                          int bh_begin, int bh_end) {
+  if (bh_begin < 0) bh_begin = 0;
+  if (bh_end > B * H) bh_end = B * H;
+  if (bh_end <= bh_begin || Sq <= 0 || Sk <= 0) return;
+  attn_ctx ctx = {q, k, v, out, lse, Sq, Sk, D, causal, bh_begin, scale};
+  parallel_for((int64_t)(bh_end - bh_begin) * Sq, 16, attn_range, &ctx);
+}

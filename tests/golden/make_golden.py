@@ -1,0 +1,143 @@
+"""Generates the golden vectors in this directory by running the REFERENCE implementations.
+
+Run once, in a container where the reference checkout is importable:
+
+    python tests/golden/make_golden.py /path/to/fast-ops
+
+It imports fast_ops.flash_attention.attention_ref.attention_ref and
+fast_ops.lion.lion_optimizer_ref.Lion from that checkout, feeds them seeded inputs and stores
+inputs (or the seed and a digest of the inputs) and outputs as .npz files.  The tests only
+read the .npz files; the reference is not needed to run them.
+
+Lion vectors are produced single-threaded on sizes that are multiples of the CPU vector width,
+because torch's CPU kernels treat the scalar `alpha` of add_ differently in their vectorised
+body and in their scalar tail, and the tail's position depends on the thread count.
+"""
+import hashlib
+import os
+import sys
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+DT = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}
+
+
+def bits(t: torch.Tensor) -> np.ndarray:
+    """Raw storage of a tensor as a numpy array (uint16 for the 16-bit types)."""
+    t = t.detach().contiguous()
+    if t.dtype in (torch.float16, torch.bfloat16):
+        return t.view(torch.int16).numpy().view(np.uint16).copy()
+    return t.numpy().copy()
+
+
+def attention_inputs(seed, B, H, Sq, Sk, D, dtype):
+    """Q, K, V ~ N(0,1) in (B,H,S,D) layout from a seeded CPU generator, cast to `dtype`."""
+    gen = torch.Generator().manual_seed(seed)
+    q = torch.randn(B, H, Sq, D, generator=gen).to(dtype)
+    k = torch.randn(B, H, Sk, D, generator=gen).to(dtype)
+    v = torch.randn(B, H, Sk, D, generator=gen).to(dtype)
+    return q, k, v
+
+
+def digest(*tensors) -> str:
+    h = hashlib.sha256()
+    for t in tensors:
+        h.update(bits(t).tobytes())
+    return h.hexdigest()
+
+
+def make_attention(attention_ref):
+    cases = [
+        # name, seed, B, H, Sq, Sk, D, input dtype, causal, row stride of the stored sample
+        ("c1_b2h4s256d64_f32_full", 0, 2, 4, 256, 256, 64, "f32", False, 4),
+        ("s384d128_bf16_causal", 1, 1, 2, 384, 384, 128, "bf16", True, 3),
+        ("s200d128_f16_causal_ragged", 2, 1, 2, 200, 200, 128, "f16", True, 1),
+        ("s131d64_bf16_full_ragged", 3, 2, 1, 131, 131, 64, "bf16", False, 1),
+        ("sq128sk320d64_f16_causal", 4, 1, 1, 128, 320, 64, "f16", True, 1),
+        ("sq300sk100d128_bf16_full", 5, 1, 1, 300, 100, 128, "bf16", False, 1),
+        ("s1024d64_bf16_causal", 6, 1, 2, 1024, 1024, 64, "bf16", True, 16),
+    ]
+    for name, seed, B, H, Sq, Sk, D, dt, causal, step in cases:
+        q, k, v = attention_inputs(seed, B, H, Sq, Sk, D, DT[dt])
+        # The reference takes (B,S,H,D); upcast=True makes it compute in fp32 and cast back
+        # to the input dtype, so feed it fp32 copies of the (already rounded) inputs.
+        qf, kf, vf = (t.float().transpose(1, 2) for t in (q, k, v))
+        out, attn = attention_ref(qf, kf, vf, causal=causal, upcast=True)
+        out = out.transpose(1, 2).contiguous()  # (B,H,Sq,D)
+        # LSE: the reference's torch path does not return it; rebuild it from the same scores
+        # and check it against the attention matrix the reference did return.
+        scores = torch.einsum("bhtd,bhsd->bhts", q.float() / (D ** 0.5), k.float())
+        if causal:
+            scores.masked_fill_(torch.triu(torch.ones(Sq, Sk, dtype=torch.bool), 1), float("-inf"))
+        lse = torch.logsumexp(scores, dim=-1)
+        assert torch.allclose(torch.exp(scores - lse[..., None]), attn, atol=2e-6), name
+        rows = np.arange(0, Sq, step)
+        np.savez_compressed(
+            os.path.join(HERE, f"attn_{name}.npz"),
+            seed=seed, shape=np.array([B, H, Sq, Sk, D]), dtype=dt, causal=causal,
+            input_sha256=digest(q, k, v), rows=rows,
+            out=out[:, :, rows, :].numpy(), lse=lse[:, :, rows].numpy())
+        print("attention", name, out.shape, "stored rows", len(rows))
+
+
+def make_lion(LionRef):
+    n = 2048
+    cases = [
+        # name, p dtype, m dtype, lr, betas, wd, p std, g std
+        ("bf16_bf16_c5like", "bf16", "bf16", 3e-5, (0.9, 0.99), 0.1, 0.02, 1e-3),
+        ("f32_bf16_c4like", "f32", "bf16", 1e-4, (0.9, 0.99), 0.1, 0.02, 1e-3),
+        ("f32_f32", "f32", "f32", 1e-4, (0.9, 0.99), 0.1, 0.02, 1e-3),
+        ("f16_f16_reftest", "f16", "f16", 1e-3, (0.9, 0.99), 0.5, 1.0, 1.0),
+        ("bf16_bf16_reftest", "bf16", "bf16", 1e-3, (0.9, 0.99), 0.0, 1.0, 1.0),
+        ("bf16_f32", "bf16", "f32", 1e-4, (0.95, 0.98), 0.1, 0.02, 1e-3),
+    ]
+    steps = 4
+    for name, pd, md, lr, betas, wd, pstd, gstd in cases:
+        gen = torch.Generator().manual_seed(sum(map(ord, name)))
+        p0 = (torch.randn(n, generator=gen) * pstd).to(DT[pd])
+        grads = [(torch.randn(n, generator=gen) * gstd).to(DT[pd]) for _ in range(steps)]
+        # Adversarial entries: zero gradient (sign(0) must be 0 on the first step), and
+        # gradients chosen so that beta1*m + (1-beta1)*g lands on or next to zero.
+        for g in grads:
+            g[:16] = 0
+        param = p0.clone().requires_grad_(True)
+        opt = LionRef([param], lr=lr, betas=betas, weight_decay=wd)
+        opt.state[param]["exp_avg"] = torch.zeros(n, dtype=DT[md])
+        ps, ms = [], []
+        for s in range(steps):
+            g = grads[s]
+            if s > 0:
+                m = opt.state[param]["exp_avg"].float()
+                cancel = (-(m * betas[0]) / (1 - betas[0])).to(DT[pd])
+                g[16:272] = cancel[16:272]
+                # one storage-type ulp to either side of the cancelling value
+                g[272:400] = torch.nextafter(cancel[272:400].float(), torch.tensor(float("inf"))).to(DT[pd])
+                g[400:528] = torch.nextafter(cancel[400:528].float(), torch.tensor(float("-inf"))).to(DT[pd])
+            param.grad = g.clone()
+            opt.step()
+            ps.append(bits(param.data))
+            ms.append(bits(opt.state[param]["exp_avg"]))
+        np.savez_compressed(
+            os.path.join(HERE, f"lion_{name}.npz"),
+            p_dtype=pd, m_dtype=md, lr=lr, betas=np.array(betas), weight_decay=wd,
+            p0=bits(p0), grads=np.stack([bits(g) for g in grads]), params=np.stack(ps),
+            exp_avgs=np.stack(ms))
+        print("lion", name, pd, md)
+
+
+def main():
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    sys.path.insert(0, ref_root)
+    from fast_ops.flash_attention.attention_ref import attention_ref
+    from fast_ops.lion.lion_optimizer_ref import Lion as LionRef
+
+    torch.set_num_threads(1)
+    make_attention(attention_ref)
+    make_lion(LionRef)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,45 @@
+"""The C-ABI library loads without a GPU and exports exactly what include/fast_ops_b200.h declares."""
+import ctypes
+import os
+import re
+
+import fast_ops_b200._lib as L
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_functions():
+    text = open(os.path.join(ROOT, "include", "fast_ops_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(fo_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_declares_the_expected_entry_points():
+    names = declared_functions()
+    for must in ("fo_flash_attn_fwd", "fo_lion_update", "fo_lion_multi_tensor_step", "fo_lion_flat_step",
+                 "fo_last_error", "fo_device_status"):
+        assert must in names
+
+
+def test_library_exports_every_declared_symbol():
+    lib = ctypes.CDLL(L.LIB_PATH) if os.path.exists(L.LIB_PATH) else L.load()
+    for name in declared_functions():
+        assert hasattr(lib, name), f"{name} is declared in the header but not exported"
+
+
+def test_python_signatures_cover_the_header():
+    assert sorted(L.SIGNATURES) == declared_functions()
+
+
+def test_version_and_error_text_need_no_gpu():
+    lib = L.load()
+    assert lib.fo_version() >= 100
+    assert lib.fo_last_error() == b""
+    # argument validation happens before any CUDA call
+    rc = lib.fo_lion_update(None, None, None, 8, L.FO_BF16, L.FO_F16, L.FO_BF16, 1e-4, 0.9, 0.99, 0.0, 0, None)
+    assert rc == -1 and b"same dtype" in lib.fo_last_error()
+    s = (ctypes.c_int64 * 3)(0, 0, 0)
+    rc = lib.fo_flash_attn_fwd(1, 1, 1, 1, None, 1, 1, 128, 128, 96, s, s, s, s, L.FO_BF16, 0, 0.1, 0, None)
+    assert rc == -3 and b"head_dim 96" in lib.fo_last_error()
+    rc = lib.fo_flash_attn_fwd(1, 1, 1, 1, None, 1, 1, 128, 128, 130, s, s, s, s, L.FO_BF16, 0, 0.1, 0, None)
+    assert rc == -1

@@ -1,0 +1,69 @@
+"""Pins the CPU oracle to vectors produced by the reference itself (tests/golden/*.npz)."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from helpers import DT, attention_inputs, from_bits, golden_files, input_digest, to_bits
+
+
+@pytest.mark.parametrize("path", golden_files("lion"), ids=lambda p: p.split("lion_")[-1][:-4])
+def test_lion_oracle_matches_reference_bit_for_bit(path):
+    z = np.load(path)
+    pd, md = DT[str(z["p_dtype"])], DT[str(z["m_dtype"])]
+    lr, betas, wd = float(z["lr"]), tuple(float(b) for b in z["betas"]), float(z["weight_decay"])
+    p = from_bits(z["p0"], pd)
+    m = torch.zeros(p.numel(), dtype=md)
+    for s in range(z["grads"].shape[0]):
+        g = from_bits(z["grads"][s], pd)
+        oracle.lion_step(p, g, m, lr, betas, wd)
+        assert np.array_equal(to_bits(p), z["params"][s]), f"param differs at step {s}"
+        assert np.array_equal(to_bits(m), z["exp_avgs"][s]), f"exp_avg differs at step {s}"
+
+
+def test_lion_oracle_sign_of_zero_is_zero():
+    # grad = 0 and momentum = 0: torch.sign(0) = 0, so only weight decay moves the parameter
+    # (fast_ops/lion/lion_optimizer_ref.py:65), unlike the reference CUDA kernel's sign(0) = -1
+    # (fast_ops/lion/lion_update.cu:10-13).
+    p = torch.full((64,), 0.5, dtype=torch.float32)
+    g = torch.zeros(64)
+    m = torch.zeros(64, dtype=torch.bfloat16)
+    oracle.lion_step(p, g, m, 1e-2, (0.9, 0.99), 0.0)
+    assert torch.equal(p, torch.full((64,), 0.5))
+    assert torch.equal(m.float(), torch.zeros(64))
+
+
+@pytest.mark.parametrize("path", golden_files("attn"), ids=lambda p: p.split("attn_")[-1][:-4])
+def test_attention_oracle_matches_reference(path):
+    z = np.load(path)
+    B, H, Sq, Sk, D = (int(x) for x in z["shape"])
+    q, k, v = attention_inputs(int(z["seed"]), B, H, Sq, Sk, D, DT[str(z["dtype"])])
+    assert input_digest(q, k, v) == str(z["input_sha256"]), "seeded inputs differ from the generator's"
+    out, lse = oracle.attention_fwd(q, k, v, causal=bool(z["causal"]))
+    rows = torch.from_numpy(z["rows"])
+    # fp32 against fp32: only the summation order differs.
+    assert torch.allclose(out[:, :, rows, :], torch.from_numpy(z["out"]), atol=2e-6, rtol=1e-5)
+    assert torch.allclose(lse[:, :, rows], torch.from_numpy(z["lse"]), atol=5e-6, rtol=1e-6)
+
+
+def test_attention_oracle_bh_range_and_empty():
+    q, k, v = attention_inputs(11, 2, 3, 40, 40, 64, torch.float32)
+    full, lse = oracle.attention_fwd(q, k, v, causal=True)
+    part, lse_p = oracle.attention_fwd(q, k, v, causal=True, bh_range=(2, 4))
+    assert torch.equal(part.view(6, 40, 64)[2:4], full.view(6, 40, 64)[2:4])
+    assert torch.equal(lse_p.view(6, 40)[2:4], lse.view(6, 40)[2:4])
+    assert part.view(6, 40, 64)[:2].abs().sum() == 0 and part.view(6, 40, 64)[4:].abs().sum() == 0
+    # causal row 0 attends to one key: out = v[0], lse = scaled score
+    assert torch.allclose(full[:, :, 0], v[:, :, 0])
+    assert torch.allclose(lse[:, :, 0], (q[:, :, 0] * k[:, :, 0]).sum(-1) / 8, atol=1e-6)
+
+
+def test_oracle_thread_count_does_not_change_results():
+    q, k, v = attention_inputs(12, 1, 2, 100, 100, 64, torch.float32)
+    n0 = oracle.num_threads()
+    a, la = oracle.attention_fwd(q, k, v)
+    oracle.set_num_threads(1)
+    b, lb = oracle.attention_fwd(q, k, v)
+    oracle.set_num_threads(0)
+    assert oracle.num_threads() == n0
+    assert torch.equal(a, b) and torch.equal(la, lb)
