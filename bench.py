@@ -1,0 +1,504 @@
+#!/usr/bin/env python
+"""Benchmark of the two hot paths on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+Prints ONE JSON line.  The headline workload is the long-context attention forward
+(B=2, H=32, S=16384, D=128, bf16, causal) per GPU: `value` is TFLOP/s summed over all ranks
+(FLOPs = 4*B*H*S*S*D/2 per rank and step), timed with CUDA events over K launches with inputs
+resident in HBM, max over ranks.  `e2e` is the same metric through the public Python call with
+pinned HOST buffers: Q, K, V copied host->device and O device->host inside the timed region.
+`also` carries the other configurations (attention at the GPT-2-small shape, the fused Lion
+step on the GPT-2-medium list and, sharded ZeRO-1 style, on the Llama-7B list).
+`cpu_baseline` times the CPU oracle (a C restatement of the reference's torch code) on a
+bounded sample of the same workload.  `--impl reference` runs only that CPU arm.
+
+Workloads: attn_c3 (default), attn_c2, lion_c4, lion_c5.
+Launch under torchrun for N > 1 (one rank per GPU); inputs are synthetic and seeded.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+ATTN = {
+    # name: (B, H, S, D, causal)
+    "attn_c2": (8, 12, 1024, 64, True),
+    "attn_c3": (2, 32, 16384, 128, True),
+    "attn_prof": (2, 32, 4096, 128, True),  # small case for profiler captures (inputs 201 MB > L2)
+}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+# ---- clocks ------------------------------------------------------------------------------------
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML (read-only) while the
+    timed region runs."""
+
+    REASONS = {
+        0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap",
+        0x80: "hw_power_brake_slowdown",
+    }
+
+    def __init__(self, index: int, period_s: float = 0.02):
+        self.index, self.period = index, period_s
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            try:  # NVML numbers GPUs without regard to CUDA_VISIBLE_DEVICES: match by UUID
+                uuid = "GPU-" + str(torch.cuda.get_device_properties(index).uuid)
+                self._h = pynvml.nvmlDeviceGetHandleByUUID(uuid)
+            except Exception:
+                self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nv = None
+
+    def _run(self):
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(self.period)
+
+    def start(self):
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None,
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ---- distributed plumbing ------------------------------------------------------------------------
+
+class Dist:
+    def __init__(self, gpus: int):
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        self.on = self.world > 1
+        if self.on:
+            import torch.distributed as dist
+
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            torch.cuda.set_device(self.local_rank)
+            dist.init_process_group("nccl", device_id=torch.device("cuda", self.local_rank))
+            self.dist = dist
+        elif gpus > 1:
+            raise SystemExit("launch with torchrun (one rank per GPU) for --gpus > 1")
+        self.device = torch.device("cuda", self.local_rank)
+        torch.cuda.set_device(self.device)
+
+    def barrier(self):
+        if self.on:
+            self.dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_ms(self, ms: float) -> float:
+        if not self.on:
+            return ms
+        t = torch.tensor([ms], device=self.device, dtype=torch.float64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def close(self):
+        if self.on:
+            self.dist.barrier()
+            self.dist.destroy_process_group()
+
+
+_flush_buf = None
+
+
+def flush_l2(device):
+    """Overwrites a 512 MB buffer (four times the 126 MB L2)."""
+    global _flush_buf
+    if _flush_buf is None or _flush_buf.device != device:
+        _flush_buf = torch.empty(512 << 20, dtype=torch.uint8, device=device)
+    _flush_buf.zero_()
+
+
+def timed_steps(d: Dist, fn, steps: int, warmup: int, sampler=None, flush=False):
+    """W untimed steps, then exactly K steps between a barrier + synchronize on both sides;
+    CUDA events on the launching (current) stream; returns the max over ranks of ms per step.
+    With `flush`, L2 is overwritten before every step and each step has its own event pair
+    (the flush is outside the events)."""
+    for _ in range(warmup):
+        fn()
+    d.barrier()
+    if sampler:
+        sampler.start()
+    if flush:
+        pairs = []
+        for _ in range(steps):
+            flush_l2(d.device)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            pairs.append((e0, e1))
+        d.barrier()
+        total = sum(a.elapsed_time(b) for a, b in pairs)
+    else:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        d.barrier()
+        total = e0.elapsed_time(e1)
+    clocks = sampler.stop() if sampler else None
+    return d.max_ms(total) / steps, clocks
+
+
+# ---- attention -------------------------------------------------------------------------------------
+
+def attn_flops(B, H, S, D, causal):
+    return 4.0 * B * H * S * S * D * (0.5 if causal else 1.0)
+
+
+def attn_inputs(B, H, S, D, device, seed):
+    gen = torch.Generator(device=device).manual_seed(seed)
+    return tuple(torch.randn(B, H, S, D, generator=gen, device=device, dtype=torch.float32).bfloat16()
+                 for _ in range(3))
+
+
+def bench_attention(d: Dist, name: str, steps: int, warmup: int, peaks, with_e2e=True, with_clocks=True):
+    import fast_ops_b200._lib as L
+    from fast_ops_b200.flash_attention import flash_attention_forward
+
+    B, H, S, D, causal = ATTN[name]
+    q, k, v = attn_inputs(B, H, S, D, d.device, seed=1000 + d.rank)
+    lib = L.load()
+    fn = lambda: flash_attention_forward(q, k, v, causal=causal)  # noqa: E731
+    launches0 = lib.fo_launch_count()
+    sampler = ClockSampler(d.local_rank) if with_clocks else None
+    input_bytes = 3 * q.numel() * 2
+    flush = input_bytes <= 2 * 126e6
+    ms, clocks = timed_steps(d, fn, steps, warmup, sampler, flush=flush)
+    launches = (lib.fo_launch_count() - launches0 - warmup)
+    if L.device_status(d.local_rank) != 0:
+        raise RuntimeError("an attention kernel reported a timed-out wait")
+    flops = attn_flops(B, H, S, D, causal)
+    tflops_rank = flops / (ms * 1e-3) / 1e12
+    out = {
+        "value": tflops_rank * d.world, "ms_per_step": ms, "gpu_launches": launches, "clocks": clocks,
+        "roofline": {"bound": "tensor", "achieved": tflops_rank, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                     "frac": tflops_rank / peaks["bf16_tflops"], "traffic": None,
+                     "peak_source": peaks["source"] + " cuBLAS bf16 burst",
+                     "frac_of_sustained": tflops_rank / peaks["bf16_tflops_sustained"]},
+        "config": {"workload": f"{name}: attention fwd B={B} H={H} S={S} D={D} bf16 causal={causal}, per GPU",
+                   "global_batch": B * d.world,
+                   "l2": ("L2 flushed (512 MB written) before every timed step" if flush
+                          else "inputs (%.0f MB) larger than L2, no flush" % (input_bytes / 1e6))},
+    }
+    if with_e2e:
+        # public call on HOST buffers: H2D of Q, K, V, forward, D2H of O, every step
+        hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
+        ho = torch.empty_like(hq).pin_memory()
+
+        def e2e_step():
+            dq, dk, dv = (t.to(d.device, non_blocking=True) for t in (hq, hk, hv))
+            ho.copy_(flash_attention_forward(dq, dk, dv, causal=causal), non_blocking=True)
+
+        e2e_steps = max(2, min(steps, 5))
+        ms_e2e, _ = timed_steps(d, e2e_step, e2e_steps, 1)
+        out["e2e"] = {"value": flops / (ms_e2e * 1e-3) / 1e12 * d.world, "unit": "TFLOP/s",
+                      "h2d_bytes_per_step": 3 * hq.numel() * 2, "d2h_bytes_per_step": ho.numel() * 2,
+                      "ms_per_step": ms_e2e, "steps": e2e_steps}
+    del q, k, v
+    return out
+
+
+def cpu_attention_sample(name: str, row_stride: int, reps: int):
+    """Times the CPU oracle on one (batch, head) slice of the workload, every `row_stride`-th
+    query row (the causal row costs are sampled evenly), all host threads."""
+    import oracle
+
+    B, H, S, D, causal = ATTN[name]
+    gen = torch.Generator().manual_seed(1)
+    q, k, v = (torch.randn(1, 1, S, D, generator=gen).bfloat16() for _ in range(3))
+    rows = range(0, S, row_stride)
+    flops = sum(4.0 * D * ((r + 1) if causal else S) for r in rows)
+    oracle.attention_fwd(q, k, v, causal=causal, row_range=(0, S, row_stride * 4))  # warm-up
+    times = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        oracle.attention_fwd(q, k, v, causal=causal, row_range=(0, S, row_stride))
+        times.append(time.perf_counter() - t0)
+    t = statistics.median(times)
+    return {"value": flops / t / 1e12, "unit": "TFLOP/s", "cores": oracle.num_threads(), "kind": "port",
+            "sample": f"{name}: one (batch, head) slice, every {row_stride}th query row "
+                      f"({flops / 1e9:.1f} GFLOP per run, median of {reps} runs of {t:.2f} s)"}, t
+
+
+# ---- Lion ------------------------------------------------------------------------------------------
+
+def gpt2_medium_shapes():
+    shapes = [(50257, 1024), (1024, 1024)]
+    for _ in range(24):
+        shapes += [(1024, 3072), (3072,), (1024, 1024), (1024,), (1024, 4096), (4096,), (4096, 1024), (1024,),
+                   (1024,), (1024,), (1024,), (1024,)]
+    return shapes
+
+
+def llama7b_shapes():
+    shapes = [(32000, 4096), (32000, 4096)]
+    for _ in range(32):
+        shapes += [(4096, 4096)] * 4 + [(11008, 4096)] * 2 + [(4096, 11008)] + [(4096,)] * 2
+    return shapes
+
+
+def numel(shape):
+    n = 1
+    for s in shape:
+        n *= s
+    return n
+
+
+def bench_lion_c4(d: Dist, steps: int, warmup: int, peaks, with_e2e=True):
+    """GPT-2-medium list: fp32 params/grads ~N(0,0.02)/N(0,1e-3), bf16 momentum, one launch per
+    step; 16 algorithmic bytes per parameter."""
+    import fast_ops_b200._lib as L
+    from fast_ops_b200.lion import Lion
+
+    gen = torch.Generator(device=d.device).manual_seed(7 + d.rank)
+    shapes = gpt2_medium_shapes()
+    params = [(torch.randn(s, generator=gen, device=d.device) * 0.02).requires_grad_(True) for s in shapes]
+    for p in params:
+        p.grad = torch.randn(p.shape, generator=gen, device=d.device) * 1e-3
+    opt = Lion(params, lr=1e-4, betas=(0.9, 0.99), weight_decay=0.1, momentum_dtype=torch.bfloat16)
+    n = sum(numel(s) for s in shapes)
+    lib = L.load()
+    l0 = lib.fo_launch_count()
+    ms, _ = timed_steps(d, opt.step, steps, warmup)
+    launches = lib.fo_launch_count() - l0 - warmup
+    gbs = n * 16 / (ms * 1e-3) / 1e9
+    # end to end: gradients arrive from pinned host memory, a parameter checksum goes back
+    hg = [p.grad.cpu().pin_memory() for p in params]
+    hres = torch.zeros(1).pin_memory()
+
+    def e2e_step():
+        for p, g in zip(params, hg):
+            p.grad.copy_(g, non_blocking=True)
+        opt.step()
+        hres.copy_(params[-1].detach().sum().reshape(1), non_blocking=True)
+
+    ms_e2e = timed_steps(d, e2e_step, 3, 1)[0] if with_e2e else float("nan")
+    res = {"workload": f"lion_c4: GPT-2-medium list, {len(shapes)} tensors, {n} params, fp32 p/g, bf16 m, per GPU",
+           "value": gbs * d.world, "unit": "GB/s", "ms_per_step": ms, "gpu_launches": launches,
+           "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                        "frac": gbs / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"] + " copy"},
+           "e2e": {"value": n * 16 / (ms_e2e * 1e-3) / 1e9 * d.world, "unit": "GB/s",
+                   "h2d_bytes_per_step": n * 4, "d2h_bytes_per_step": 4, "ms_per_step": ms_e2e}}
+    del params, opt, hg
+    torch.cuda.empty_cache()
+    return res
+
+
+def bench_lion_c5(d: Dist, steps: int, warmup: int, peaks):
+    """Llama-7B list, bf16 p/g/m, 10 algorithmic bytes per parameter, ZeRO-1: each rank updates
+    1/N of one flat buffer, then ONE NCCL all-gather of the updated bf16 weights.  Total work is
+    fixed as N grows."""
+    import fast_ops_b200._lib as L
+    from fast_ops_b200.lion import FlatLayout
+    from fast_ops_b200.lion.lion_optimizer import _flat_step
+
+    shapes = llama7b_shapes()
+    layout = FlatLayout.build([numel(s) for s in shapes], d.world)
+    n = sum(numel(s) for s in shapes)
+    total = layout.total
+    gen = torch.Generator(device=d.device).manual_seed(11)
+    flat_p = torch.empty(total, device=d.device, dtype=torch.bfloat16)
+    flat_g = torch.empty(total, device=d.device, dtype=torch.bfloat16)
+    piece = 1 << 28
+    for off in range(0, total, piece):  # bounded temporaries
+        m = min(piece, total - off)
+        flat_p[off:off + m] = (torch.randn(m, generator=gen, device=d.device) * 0.02).bfloat16()
+        flat_g[off:off + m] = (torch.randn(m, generator=gen, device=d.device) * 1e-3).bfloat16()
+    begin, end = layout.shard_range(d.rank)
+    m_shard = torch.zeros(end - begin, device=d.device, dtype=torch.bfloat16)
+    lib = L.load()
+
+    def step_kernel():
+        _flat_step(flat_p, flat_g, m_shard, begin, end, 3e-5, (0.9, 0.99), 0.1)
+
+    def gather():
+        if d.on:
+            d.dist.all_gather_into_tensor(flat_p, flat_p[begin:end])
+
+    def full_step():
+        step_kernel()
+        gather()
+
+    l0 = lib.fo_launch_count()
+    ms_full, _ = timed_steps(d, full_step, steps, warmup)
+    launches = lib.fo_launch_count() - l0 - warmup
+    ms_kernel, _ = timed_steps(d, step_kernel, steps, 1)
+    ms_gather = timed_steps(d, gather, steps, 1)[0] if d.on else 0.0
+    shard_bytes = (end - begin) * 10
+    res = {"workload": f"lion_c5: Llama-7B list, {len(shapes)} tensors, {n} params, bf16 p/g/m, ZeRO-1 over "
+                       f"{d.world} GPU(s) + all-gather of bf16 weights",
+           "scaling": "strong",
+           "value": n * 10 / (ms_full * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms_full, "gpu_launches": launches,
+           "kernel_ms": ms_kernel, "kernel_gbs_per_gpu": shard_bytes / (ms_kernel * 1e-3) / 1e9,
+           "roofline": {"bound": "hbm", "achieved": shard_bytes / (ms_kernel * 1e-3) / 1e9, "peak": peaks["hbm_gbs"],
+                        "unit": "GB/s", "frac": shard_bytes / (ms_kernel * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                        "traffic": None, "peak_source": peaks["source"] + " copy"}}
+    if d.on:
+        recv = (d.world - 1) / d.world * total * 2
+        res["all_gather"] = {"ms": ms_gather, "bus_gbs": recv / (ms_gather * 1e-3) / 1e9,
+                             "bytes_received_per_gpu": recv}
+    del flat_p, flat_g, m_shard
+    torch.cuda.empty_cache()
+    return res
+
+
+def cpu_lion_sample(reps: int):
+    """Times the CPU oracle's Lion step on the first tensor of the GPT-2-medium list (wte)."""
+    import oracle
+
+    n = 50257 * 1024
+    gen = torch.Generator().manual_seed(2)
+    p = torch.randn(n, generator=gen) * 0.02
+    g = torch.randn(n, generator=gen) * 1e-3
+    m = torch.zeros(n, dtype=torch.bfloat16)
+    oracle.lion_step(p, g, m, 1e-4, (0.9, 0.99), 0.1)
+    times = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        oracle.lion_step(p, g, m, 1e-4, (0.9, 0.99), 0.1)
+        times.append(time.perf_counter() - t0)
+    t = statistics.median(times)
+    return {"value": n * 16 / t / 1e9, "unit": "GB/s", "cores": oracle.num_threads(), "kind": "port",
+            "sample": f"lion_c4: the 50257x1024 embedding only ({n} params), median of {reps} steps of {t:.3f} s"}
+
+
+# ---- main ------------------------------------------------------------------------------------------
+
+def run_reference_arm(args):
+    """CPU arm: the oracle (a C port of the reference's torch code) on the host cores, on a
+    bounded sample of the workload per step.  Rank 0 only."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    name = args.workload
+    if name.startswith("attn"):
+        stride = 4 if name == "attn_c3" else 1
+        cpu, _ = cpu_attention_sample(name, stride, max(1, args.steps))
+        B, H, S, D, causal = ATTN[name]
+        work = f"{name}: attention fwd B={B} H={H} S={S} D={D} bf16 causal={causal}, per GPU"
+        metric, unit = "attention_fwd_tflops", "TFLOP/s"
+    else:
+        cpu = cpu_lion_sample(max(1, args.steps))
+        work, metric, unit = name, "lion_step_hbm_gbs", "GB/s"
+    line = {"impl": "reference", "metric": metric, "value": cpu["value"], "unit": unit, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": {"workload": work},
+            "cpu_baseline": cpu,
+            "e2e": {"value": cpu["value"], "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default="attn_c3", choices=["attn_c3", "attn_c2", "attn_prof", "lion_c4", "lion_c5"])
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-also", action="store_true", help="skip the secondary workloads")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU path (use --impl reference for the CPU arm)")
+
+    peaks = load_peaks()
+    d = Dist(args.gpus)
+    line = {"n_gpus": d.world, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True,
+            "vs_baseline": None, "data": "synthetic"}
+    if args.workload.startswith("attn"):
+        r = bench_attention(d, args.workload, args.steps, args.warmup, peaks, with_e2e=not args.no_e2e)
+        line.update({"metric": "attention_fwd_tflops", "unit": "TFLOP/s", "scaling": "weak", "dtype": "bf16"})
+        line.update(r)
+    elif args.workload == "lion_c4":
+        r = bench_lion_c4(d, args.steps, args.warmup, peaks, with_e2e=not args.no_e2e)
+        line.update({"metric": "lion_step_hbm_gbs", "scaling": "weak", "dtype": "f32",
+                     "config": {"workload": r.pop("workload"), "l2": "5.7 GB per step, larger than L2"}})
+        line.update(r)
+    else:
+        r = bench_lion_c5(d, args.steps, args.warmup, peaks)
+        line.update({"metric": "lion_step_hbm_gbs", "dtype": "bf16",
+                     "config": {"workload": r.pop("workload"), "l2": "67 GB per step, larger than L2"}})
+        line.update(r)
+
+    if not args.no_also:
+        also = {}
+        if args.workload != "attn_c2":
+            a = bench_attention(d, "attn_c2", max(args.steps, 50), args.warmup, peaks, with_e2e=False, with_clocks=False)
+            also["attn_c2"] = {k: a[k] for k in ("value", "ms_per_step", "roofline", "config")}
+            also["attn_c2"]["unit"] = "TFLOP/s"
+        if args.workload != "lion_c4":
+            also["lion_c4"] = bench_lion_c4(d, args.steps, args.warmup, peaks)
+        if args.workload != "lion_c5":
+            also["lion_c5"] = bench_lion_c5(d, max(3, args.steps // 4), 2, peaks)
+        line["also"] = also
+
+    if d.rank == 0 and d.world == 1 and not args.no_cpu:
+        if args.workload.startswith("attn"):
+            line["cpu_baseline"], _ = cpu_attention_sample(args.workload, 1, 3)
+            if not args.no_also:
+                line["also"]["lion_c4"]["cpu_baseline"] = cpu_lion_sample(3)
+        else:
+            line["cpu_baseline"] = cpu_lion_sample(3)
+    d.close()
+    if d.rank == 0:
+        print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -41,6 +41,20 @@ def lion_update(param: Tensor, grad: Tensor, exp_avg: Tensor, lr: float, beta1: 
         _lib.current_stream_ptr(param.device)))
 
 
+def _is_dense(t: Tensor) -> bool:
+    """True when the tensor's elements fill one gap-free block of memory in some order
+    (the reference's `is_non_overlapping_and_dense`, fast_ops/lion/lion_update.cu:109-112)."""
+    if t.is_contiguous() or t.numel() == 0:
+        return True
+    strides = sorted((st, sz) for st, sz in zip(t.stride(), t.shape) if sz != 1)
+    expect = 1
+    for st, sz in strides:
+        if st != expect:
+            return False
+        expect *= sz
+    return True
+
+
 def _check_triple(param: Tensor, grad: Tensor, exp_avg: Tensor) -> None:
     if not param.is_cuda:
         raise RuntimeError("fast_ops_b200 Lion needs CUDA tensors (there is no CPU path)")
@@ -51,7 +65,7 @@ def _check_triple(param: Tensor, grad: Tensor, exp_avg: Tensor) -> None:
     if grad.shape != param.shape or exp_avg.numel() != param.numel():
         raise RuntimeError("param, grad and exp_avg must have the same number of elements")
     for t in (param, grad, exp_avg):
-        if not t.is_non_overlapping_and_dense():
+        if not _is_dense(t):
             raise RuntimeError("expected tensor to be contiguous")
     if param.stride() != grad.stride():
         raise RuntimeError("param and grad must share a memory layout")

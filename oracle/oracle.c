@@ -185,11 +185,14 @@ void oracle_lion_step(void* param, const void* grad, void* exp_avg, int64_t nume
  * fp32 or NULL.  `scale` multiplies q before the dot products (attention_ref.py:46 divides q
  * by sqrt(d); pass 1/sqrt(d)).  Causal masking is top-left aligned: column j > row i is
  * -inf (attention_ref.py:54-58).  `bh_begin/bh_end` restrict the work to a range of flattened
- * (batch, head) pairs so that a bounded sample of a large problem can be timed. */
+ * (batch, head) pairs, and `row_begin/row_end/row_stride` to query rows row_begin,
+ * row_begin+row_stride, ... < row_end of each pair, so that a bounded sample of a large problem
+ * can be checked or timed; rows outside the sample are left untouched. */
 typedef struct {
   const float *q, *k, *v;
   float *out, *lse;
   int Sq, Sk, D, causal, bh_begin;
+  int row_begin, row_stride, rows_per_bh;
   float scale;
 } attn_ctx;
 
@@ -204,8 +207,8 @@ static void attn_range(int64_t begin, int64_t end, void* vctx) {
     float* qs = (float*)malloc(sizeof(float) * (size_t)D);
     float* acc = (float*)malloc(sizeof(float) * (size_t)D);
     for (int64_t r = begin; r < end; ++r) {
-      const int bh = bh_begin + (int)(r / Sq);
-      const int i = (int)(r % Sq);
+      const int bh = bh_begin + (int)(r / c->rows_per_bh);
+      const int i = c->row_begin + (int)(r % c->rows_per_bh) * c->row_stride;
       const float* qi = q + ((int64_t)bh * Sq + i) * D;
       const float* kb = k + (int64_t)bh * Sk * D;
       const float* vb = v + (int64_t)bh * Sk * D;
@@ -247,10 +250,14 @@ static void attn_range(int64_t begin, int64_t end, void* vctx) {
 
 void oracle_attention_fwd(const float* q, const float* k, const float* v, float* out, float* lse,
                           int B, int H, int Sq, int Sk, int D, int causal, float scale,
-                          int bh_begin, int bh_end) {
+                          int bh_begin, int bh_end, int row_begin, int row_end, int row_stride) {
   if (bh_begin < 0) bh_begin = 0;
   if (bh_end > B * H) bh_end = B * H;
-  if (bh_end <= bh_begin || Sq <= 0 || Sk <= 0) return;
-  attn_ctx ctx = {q, k, v, out, lse, Sq, Sk, D, causal, bh_begin, scale};
-  parallel_for((int64_t)(bh_end - bh_begin) * Sq, 16, attn_range, &ctx);
+  if (row_begin < 0) row_begin = 0;
+  if (row_end > Sq) row_end = Sq;
+  if (row_stride < 1) row_stride = 1;
+  if (bh_end <= bh_begin || row_end <= row_begin || Sk <= 0) return;
+  const int rows_per_bh = (row_end - row_begin + row_stride - 1) / row_stride;
+  attn_ctx ctx = {q, k, v, out, lse, Sq, Sk, D, causal, bh_begin, row_begin, row_stride, rows_per_bh, scale};
+  parallel_for((int64_t)(bh_end - bh_begin) * rows_per_bh, 16, attn_range, &ctx);
 }

@@ -39,7 +39,7 @@ def _load() -> ctypes.CDLL:
         lib.oracle_attention_fwd.argtypes = [
             ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
             ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
-            ctypes.c_float, ctypes.c_int, ctypes.c_int]
+            ctypes.c_float, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int]
         lib.oracle_attention_fwd.restype = None
         lib.oracle_num_threads.restype = ctypes.c_int
         lib.oracle_set_num_threads.argtypes = [ctypes.c_int]
@@ -72,13 +72,15 @@ def lion_step(param: torch.Tensor, grad: torch.Tensor, exp_avg: torch.Tensor, lr
 
 def attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = False,
                   softmax_scale: Optional[float] = None,
-                  bh_range: Optional[Tuple[int, int]] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+                  bh_range: Optional[Tuple[int, int]] = None,
+                  row_range: Optional[Tuple[int, int, int]] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """softmax(scale * q k^T [+ causal mask]) v in fp32 on the CPU.
 
     q: (B,H,Sq,D), k/v: (B,H,Sk,D), any float dtype (upcast to fp32 first, as
     fast_ops/flash_attention/attention_ref.py:41-43 does).  Returns (out, lse), both fp32;
     out is (B,H,Sq,D), lse is (B,H,Sq).  With `bh_range=(b, e)` only the flattened
-    (batch*head) slices b..e-1 are computed; the rest of the outputs is left zero.
+    (batch*head) slices b..e-1 are computed, and with `row_range=(begin, end, stride)` only
+    those query rows of each slice; the rest of the outputs is left zero.
     """
     B, H, Sq, D = q.shape
     Sk = k.shape[2]
@@ -88,6 +90,8 @@ def attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: boo
     out = torch.zeros(B, H, Sq, D, dtype=torch.float32)
     lse = torch.zeros(B, H, Sq, dtype=torch.float32)
     b, e = bh_range if bh_range is not None else (0, B * H)
+    r0, r1, rs = row_range if row_range is not None else (0, Sq, 1)
     _load().oracle_attention_fwd(qf.data_ptr(), kf.data_ptr(), vf.data_ptr(), out.data_ptr(), lse.data_ptr(),
-                                 B, H, Sq, Sk, D, int(bool(causal)), float(softmax_scale), int(b), int(e))
+                                 B, H, Sq, Sk, D, int(bool(causal)), float(softmax_scale), int(b), int(e),
+                                 int(r0), int(r1), int(rs))
     return out, lse

@@ -67,3 +67,14 @@ def test_oracle_thread_count_does_not_change_results():
     oracle.set_num_threads(0)
     assert oracle.num_threads() == n0
     assert torch.equal(a, b) and torch.equal(la, lb)
+
+
+def test_attention_oracle_row_sampling():
+    q, k, v = attention_inputs(13, 1, 2, 50, 50, 64, torch.float32)
+    full, lse = oracle.attention_fwd(q, k, v, causal=True)
+    part, lse_p = oracle.attention_fwd(q, k, v, causal=True, row_range=(3, 47, 5))
+    rows = list(range(3, 47, 5))
+    assert torch.equal(part[:, :, rows], full[:, :, rows]) and torch.equal(lse_p[:, :, rows], lse[:, :, rows])
+    mask = torch.ones(50, dtype=torch.bool)
+    mask[rows] = False
+    assert part[:, :, mask].abs().sum() == 0
