@@ -35,6 +35,10 @@ SIGNATURES = {
     "fo_lion_multi_tensor_step": (_c.c_int, [_c.POINTER(_PTR), _c.POINTER(_PTR), _c.POINTER(_PTR), _I64P, _c.c_int,
                                              _c.c_int, _c.c_int, _c.c_int,
                                              _c.c_double, _c.c_double, _c.c_double, _c.c_double, _c.c_int, _PTR]),
+    "fo_lion_multi_tensor_step_noalloc": (_c.c_int, [_c.POINTER(_PTR), _c.POINTER(_PTR), _c.POINTER(_PTR), _I64P,
+                                                     _c.c_int, _c.c_int, _c.c_int, _c.c_int,
+                                                     _c.c_double, _c.c_double, _c.c_double, _c.c_double,
+                                                     _c.c_int, _PTR]),
     "fo_lion_flat_step": (_c.c_int, [_PTR, _PTR, _PTR, _c.c_int64, _c.c_int64, _c.c_int, _c.c_int, _c.c_int,
                                      _c.c_double, _c.c_double, _c.c_double, _c.c_double, _c.c_int, _PTR]),
     "fo_lion_clear_cache": (_c.c_int, []),

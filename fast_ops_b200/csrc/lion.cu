@@ -399,3 +399,101 @@ extern "C" int fo_lion_flat_step(void* param, const void* grad, void* exp_avg_sh
   return fo_lion_update(p, g, exp_avg_shard, end - begin, p_dtype, g_dtype, m_dtype, lr, beta1, beta2,
                         weight_decay, device, stream);
 }
+
+// ---- allocation-free variant -----------------------------------------------------------------
+//
+// fo_lion_multi_tensor_step builds its device tensor table with cudaMalloc the first time it sees
+// a pointer list.  Some callers cannot afford that: a trainer that has already handed every byte
+// of device memory to its own pool (cudaMalloc then fails), or a step loop that must never hit
+// the device-wide synchronisation an allocation or a free can imply.  For them the same kernel
+// runs with its table in a fixed array that is part of the library image: nothing is allocated,
+// on the device or through any allocating library routine.
+//
+// The array is a file-scope __device__ object, so every device that loads the library carries
+// its kNoAllocTableBytes (about 40 KiB) until the process exits.  In host code the array's name is
+// only a handle: the device address comes from cudaGetSymbolAddress, looked up once per device
+// with that device current, and that address is what the kernel receives.
+
+namespace {
+
+constexpr int kNoAllocMaxTensors = 1024;
+constexpr size_t kNoAllocTableBytes =
+    ((sizeof(LionTensor) * kNoAllocMaxTensors + sizeof(int64_t) * (kNoAllocMaxTensors + 1)) + 255) / 256 * 256;
+
+static __device__ __align__(256) unsigned char g_noalloc_table[kNoAllocTableBytes];
+
+constexpr int kNoAllocMaxDevices = 64;
+std::mutex g_noalloc_mutex;
+void* g_noalloc_dev_ptr[kNoAllocMaxDevices] = {};  // device address of g_noalloc_table, per device
+// Host image of the table; guarded by g_noalloc_mutex.  cudaMemcpyAsync from pageable memory has
+// taken its copy of the source by the time it returns, so the image can be reused by the next call.
+alignas(16) unsigned char g_noalloc_host[kNoAllocTableBytes];
+
+}  // namespace
+
+extern "C" int fo_lion_multi_tensor_step_noalloc(void* const* params, const void* const* grads,
+                                                 void* const* exp_avgs, const int64_t* numels, int n_tensors,
+                                                 int p_dtype, int g_dtype, int m_dtype,
+                                                 double lr, double beta1, double beta2, double weight_decay,
+                                                 int device, void* stream) {
+  fo::clear_error();
+  if (int rc = check_dtypes(p_dtype, g_dtype, m_dtype)) return rc;
+  FO_REQUIRE(n_tensors >= 0, "n_tensors must be >= 0");
+  if (n_tensors == 0) return FO_OK;
+  FO_REQUIRE(params && grads && exp_avgs && numels, "null tensor list");
+  FO_REQUIRE(n_tensors <= kNoAllocMaxTensors,
+             "the allocation-free Lion step takes at most %d tensors per call (got %d); split the list or use "
+             "fo_lion_multi_tensor_step",
+             kNoAllocMaxTensors, n_tensors);
+  FO_REQUIRE(device >= 0 && device < kNoAllocMaxDevices, "device index %d outside [0, %d)", device,
+             kNoAllocMaxDevices);
+  LionConsts c;
+  if (int rc = make_consts(lr, beta1, beta2, weight_decay, p_dtype, m_dtype, &c)) return rc;
+
+  fo::DeviceGuard guard(device);
+  FO_REQUIRE(guard.ok, "cannot make device %d current", device);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (g_noalloc_dev_ptr[device] == nullptr) {
+    // First call on this device: resolve the array's device address (the device is current).
+    void* ptr = nullptr;
+    FO_CUDA_CHECK(cudaGetSymbolAddress(&ptr, g_noalloc_table));
+    FO_REQUIRE(ptr != nullptr, "cudaGetSymbolAddress returned a null address");
+    g_noalloc_dev_ptr[device] = ptr;
+  }
+  void* d_table = g_noalloc_dev_ptr[device];
+
+  // Compact the list (empty tensors carry no work) straight into the host image.
+  int n = 0;
+  for (int i = 0; i < n_tensors; ++i) {
+    FO_REQUIRE(numels[i] >= 0, "tensor %d has negative numel", i);
+    if (numels[i] > 0) {
+      FO_REQUIRE(params[i] && grads[i] && exp_avgs[i], "tensor %d has a null pointer", i);
+      ++n;
+    }
+  }
+  if (n == 0) return FO_OK;
+  LionTensor* tensors = reinterpret_cast<LionTensor*>(g_noalloc_host);
+  int64_t* chunk_start = reinterpret_cast<int64_t*>(tensors + n);
+  int64_t total = 0;
+  int k = 0;
+  for (int i = 0; i < n_tensors; ++i) {
+    if (numels[i] == 0) continue;
+    tensors[k] = LionTensor{params[i], grads[i], exp_avgs[i], numels[i]};
+    chunk_start[k] = total;
+    total += (numels[i] + kChunk - 1) / kChunk;
+    ++k;
+  }
+  chunk_start[n] = total;
+  const size_t bytes = sizeof(LionTensor) * n + sizeof(int64_t) * (n + 1);
+  // Every entry the kernel reads is rewritten here, so nothing left by an earlier call is used.
+  FO_CUDA_CHECK(cudaMemcpyAsync(d_table, g_noalloc_host, bytes, cudaMemcpyHostToDevice, s));
+
+  Plan plan;
+  plan.device = device;
+  plan.n_tensors = n;
+  plan.total_chunks = total;
+  plan.d_blob = d_table;
+  return launch(plan, p_dtype, m_dtype, c, s);
+}

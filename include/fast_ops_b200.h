@@ -117,6 +117,29 @@ int fo_lion_flat_step(void* param, const void* grad, void* exp_avg_shard,
                       double lr, double beta1, double beta2, double weight_decay,
                       int device, void* stream);
 
+/*
+ * fo_lion_multi_tensor_step for callers that must not allocate: same arguments, same kernel,
+ * same results, but the device-side tensor table lives in a fixed array inside the library
+ * (about 40 KiB per device that loads the library, held until the process exits) instead of
+ * memory obtained with cudaMalloc.  Meant for a step loop whose owner has given all device
+ * memory to its own pool, or that cannot tolerate the device-wide synchronisation an
+ * allocation may cause.  It has no counterpart in the reference.
+ *
+ *   - At most 1024 tensors per call; a longer list is rejected with FO_ERR_INVALID_ARGUMENT
+ *     (split it, or use fo_lion_multi_tensor_step).
+ *   - It calls no cudaMalloc, cudaFree or other allocating routine.  The first call on a device
+ *     looks up the array's device address; make that first call outside any stream capture.
+ *   - The table is copied to the device on `stream` on every call, ahead of the kernel.  All
+ *     calls on a device share the one array and every call rewrites the entries it uses:
+ *     calls on the same stream are ordered, but two calls whose kernels can overlap on the GPU
+ *     (different streams without an event between them) race on the table.
+ */
+int fo_lion_multi_tensor_step_noalloc(void* const* params, const void* const* grads,
+                                      void* const* exp_avgs, const int64_t* numels, int n_tensors,
+                                      int p_dtype, int g_dtype, int m_dtype,
+                                      double lr, double beta1, double beta2, double weight_decay,
+                                      int device, void* stream);
+
 /* Drops the cached tensor tables of fo_lion_multi_tensor_step (all devices). */
 int fo_lion_clear_cache(void);
 
