@@ -10,7 +10,8 @@ import os
 import threading
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libfast_ops_b200.so")
+# FO_B200_LIB points the loader at another build of the same library (kernel tuning).
+LIB_PATH = os.environ.get("FO_B200_LIB") or os.path.join(_HERE, "libfast_ops_b200.so")
 
 FO_F16, FO_BF16, FO_F32 = 0, 1, 2
 
@@ -43,6 +44,8 @@ SIGNATURES = {
                                      _c.c_double, _c.c_double, _c.c_double, _c.c_double, _c.c_int, _PTR]),
     "fo_lion_clear_cache": (_c.c_int, []),
     "fo_launch_count": (_c.c_int64, []),
+    "fo_debug_set_attn_trace": (_c.c_int, [_PTR]),
+    "fo_debug_attn_trace_shape": (_c.c_int, [_c.POINTER(_c.c_int), _c.POINTER(_c.c_int), _c.POINTER(_c.c_int)]),
     "fo_debug_umma_tile": (_c.c_int, [_PTR, _PTR, _PTR, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _PTR]),
 }
 

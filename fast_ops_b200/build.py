@@ -40,11 +40,12 @@ def is_stale() -> bool:
     return any(os.path.getmtime(f) > t for f in _deps())
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    if not force and not is_stale():
+def build(force: bool = False, verbose: bool = False, out: str = LIB, defines=()) -> str:
+    """Builds the library; `defines` ("NAME=VALUE", ...) and `out` produce tuning variants."""
+    if not force and out == LIB and not is_stale():
         return LIB
     nvcc = os.environ.get("NVCC", "nvcc")
-    cmd = [nvcc] + NVCC_FLAGS + ["-o", LIB] + sources()
+    cmd = [nvcc] + NVCC_FLAGS + ["-D" + d for d in defines] + ["-o", out] + sources()
     proc = subprocess.run(cmd, capture_output=True, text=True)
     log = proc.stdout + proc.stderr
     with open(os.path.join(HERE, "build.log"), "w") as f:
@@ -53,7 +54,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         raise RuntimeError("nvcc failed:\n" + log[-4000:])
     if verbose:
         print(log)
-    return LIB
+    return out
 
 
 if __name__ == "__main__":

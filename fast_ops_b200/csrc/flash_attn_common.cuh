@@ -23,7 +23,18 @@ struct AttnParams {
   float scale_log2;  // softmax_scale * log2(e)
   int* device_status;
   int num_q_tiles;
+  // Optional timeline of CTA 0 (debug): [role][key tile][event] SM clock values, or null.
+  unsigned long long* trace;
 };
+
+constexpr int kTraceRoles = 3;   // softmax tile 0, softmax tile 1, MMA issuer
+constexpr int kTraceIters = 160;
+constexpr int kTraceEvents = 6;
+
+__device__ __forceinline__ void trace_event(const AttnParams& prm, int role, int j, int ev) {
+  if (prm.trace != nullptr && blockIdx.x == 0 && (threadIdx.x & 31) == 0 && j < kTraceIters)
+    prm.trace[(role * kTraceIters + j) * kTraceEvents + ev] = clock64();
+}
 
 // Descriptor of the kk-th K=16 slice of a K-major [128 x D] tile stored as D/64 boxes.
 __device__ __forceinline__ uint64_t kmajor_desc(uint32_t tile_smem, int kk) {

@@ -153,7 +153,7 @@ umma_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   for (int cb = 0; cb < N; cb += 32) {
     uint32_t regs[32];
     tmem_ld32(tC + lane_base + cb, regs);
-    tcgen05_wait_ld();
+    tmem_ld_wait(regs);
 #pragma unroll
     for (int i = 0; i < 32; ++i) c[static_cast<size_t>(tid) * N + cb + i] = __uint_as_float(regs[i]);
   }
@@ -167,6 +167,9 @@ int set_smem(Kernel kernel, int bytes) {
   FO_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
   return FO_OK;
 }
+
+// Debug timeline buffer handed to the next attention launches (null = off).
+unsigned long long* g_attn_trace = nullptr;
 
 enum class AttnImpl { kSimple, kWarpSpecialized };
 
@@ -237,6 +240,7 @@ extern "C" int fo_flash_attn_fwd(const void* q, const void* k, const void* v, vo
   prm.scale_log2 = softmax_scale * 1.4426950408889634f;
   prm.device_status = status;
   prm.num_q_tiles = (Sq + kBlockM - 1) / kBlockM;
+  prm.trace = g_attn_trace;
 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool bf16 = dtype == FO_BF16;
@@ -277,5 +281,17 @@ extern "C" int fo_debug_umma_tile(const void* a, const void* b, float* c, int N,
   }
   fo::g_launch_count.fetch_add(1, std::memory_order_relaxed);
   FO_CUDA_CHECK(cudaGetLastError());
+  return FO_OK;
+}
+
+extern "C" int fo_debug_set_attn_trace(void* device_buffer) {
+  g_attn_trace = static_cast<unsigned long long*>(device_buffer);
+  return FO_OK;
+}
+
+extern "C" int fo_debug_attn_trace_shape(int* roles, int* iters, int* events) {
+  *roles = fo::kTraceRoles;
+  *iters = fo::kTraceIters;
+  *events = fo::kTraceEvents;
   return FO_OK;
 }

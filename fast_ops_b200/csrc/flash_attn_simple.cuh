@@ -119,7 +119,8 @@ attn_fwd_simple_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     uint32_t sr[4][32];
 #pragma unroll
     for (int c = 0; c < 4; ++c) tmem_ld32(tS + lane_base + c * 32, sr[c]);
-    tcgen05_wait_ld();
+#pragma unroll
+    for (int c = 0; c < 4; ++c) tmem_ld_wait(sr[c]);
 
     const bool need_mask = (k0 + kBlockN > prm.Sk) || (prm.causal && k0 + kBlockN - 1 > q0);
     float mx = -INFINITY;
@@ -160,7 +161,7 @@ attn_fwd_simple_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       for (int c = 0; c < D / 32; ++c) {
         uint32_t orr[32];
         tmem_ld32(tO + lane_base + c * 32, orr);
-        tcgen05_wait_ld();
+        tmem_ld_wait(orr);
 #pragma unroll
         for (int i = 0; i < 32; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
         tmem_st32(tO + lane_base + c * 32, orr);
@@ -197,7 +198,7 @@ attn_fwd_simple_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     uint32_t orr[32];
     if (n_kv > 0) {
       tmem_ld32(tO + lane_base + c * 32, orr);
-      tcgen05_wait_ld();
+      tmem_ld_wait(orr);
     } else {
 #pragma unroll
       for (int i = 0; i < 32; ++i) orr[i] = 0;

@@ -23,6 +23,27 @@
 
 namespace fo {
 
+// Tuning switches of the softmax warps (compile-time; the defaults are the measured best).
+#ifndef FO_WS_PIPE_LD
+#define FO_WS_PIPE_LD 1  // 1: overlap each tensor-memory load with the row max of the previous chunk
+#endif
+#ifndef FO_WS_MAX3
+#define FO_WS_MAX3 1  // 3-input max
+#endif
+#ifndef FO_WS_EMU_PAIRS
+#define FO_WS_EMU_PAIRS 0  // of every 8 column pairs, how many use the polynomial exp2 (0..8)
+#endif
+#ifndef FO_WS_P_F16
+#define FO_WS_P_F16 0  // 1: exponentials from the packed-half ex2 (two per instruction); 0: fp32 ex2
+#endif
+
+#ifndef FO_WS_P_PIECES
+#define FO_WS_P_PIECES 1  // pieces (1, 2 or 4) in which P is handed to the MMA issuer
+#endif
+constexpr int kPPieces = FO_WS_P_PIECES;
+constexpr int kEmuPairs = FO_WS_EMU_PAIRS;
+constexpr int kMaxPPieces = 4;
+
 template <int D>
 struct WsConfig {
   static constexpr int kTileBytes = kBlockM * D * 2;
@@ -33,7 +54,7 @@ struct WsConfig {
   static constexpr int kOffAlpha = kOffKV + kStages * kTileBytes;  // [2 tiles][2 buffers][128] float
   static constexpr int kOffFinal = kOffAlpha + 2 * 2 * 128 * 4;    // [2 tiles][l, m][128] float
   static constexpr int kOffBars = kOffFinal + 2 * 2 * 128 * 4;
-  static constexpr int kNumBars = 1 + 2 * kStages + 2 * 6;
+  static constexpr int kNumBars = 1 + 2 * kStages + 2 * 5 + 2 * kMaxPPieces;
   static constexpr int kOffMisc = kOffBars + kNumBars * 8;
   static constexpr int kSmemBytes = kOffMisc + 64 + 1024 /* alignment slack */;
   static constexpr uint32_t kTmemCols = 512;
@@ -44,6 +65,8 @@ struct WsConfig {
 // units): exp2 arguments then stay below 8, P stays below 256, and most key tiles need no
 // rescaling of O at all.
 constexpr float kRescaleThreshold = 8.0f;
+
+
 
 template <int kRegs> __device__ __forceinline__ void reg_alloc() {
   asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs));
@@ -74,8 +97,8 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   uint64_t* bar_kv_full = bars + 1;             // [kStages] TMA -> MMA
   uint64_t* bar_kv_empty = bar_kv_full + kStages;  // [kStages] MMA -> TMA
   uint64_t* bar_s_full = bar_kv_empty + kStages;   // [2] MMA -> softmax
-  uint64_t* bar_p_full = bar_s_full + 2;           // [2] softmax -> MMA (128 arrivals)
-  uint64_t* bar_o_full = bar_p_full + 2;           // [2] MMA -> correction
+  uint64_t* bar_p_full = bar_s_full + 2;           // [2 tiles][kMaxPPieces] softmax -> MMA (128 arrivals)
+  uint64_t* bar_o_full = bar_p_full + 2 * kMaxPPieces;  // [2] MMA -> correction
   uint64_t* bar_corr = bar_o_full + 2;             // [2] softmax -> correction (128 arrivals)
   uint64_t* bar_o_scaled = bar_corr + 2;           // [2] correction -> MMA (128 arrivals)
   // [2] softmax -> correction, once: final row sum and maximum are in shared memory.  A barrier
@@ -110,7 +133,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar_s_full + s, 1);
-      mbar_init(bar_p_full + s, 128);
+      for (int i = 0; i < kMaxPPieces; ++i) mbar_init(bar_p_full + kMaxPPieces * s + i, 128);
       mbar_init(bar_o_full + s, 1);
       mbar_init(bar_corr + s, 128);
       mbar_init(bar_o_scaled + s, 128);
@@ -151,56 +174,129 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       const int k0 = j * kBlockN;
       mbar_wait(bar_s_full + s, j & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_MMA);
       tcgen05_fence_after_sync();
+      if ((warp & 3) == 0) trace_event(prm, s, j, 0);
+      const bool need_mask = (k0 + kBlockN > prm.Sk) || (prm.causal && k0 + kBlockN - 1 > q0);
       uint32_t sr[4][32];
+      float mxa = -INFINITY, mxb = -INFINITY, mxc = -INFINITY, mxd = -INFINITY;
+#if FO_WS_PIPE_LD == 2
+      // two loads in flight: chunks 0,1, then chunks 2,3 while 0,1 are reduced
+      tmem_ld32(tS, sr[0]);
+      tmem_ld32(tS + 32, sr[1]);
+      tmem_ld_wait(sr[0]);
+      tmem_ld_wait(sr[1]);
+      tmem_ld32(tS + 64, sr[2]);
+      tmem_ld32(tS + 96, sr[3]);
+      if ((warp & 3) == 0) trace_event(prm, s, j, 4);
+#elif FO_WS_PIPE_LD == 1
+      // Tensor-memory loads are software-pipelined against the row maximum: chunk c+1 is in
+      // flight while chunk c is reduced.
+      tmem_ld32(tS, sr[0]);
+      tmem_ld_wait(sr[0]);
+      if ((warp & 3) == 0) trace_event(prm, s, j, 4);
+#else
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, sr[c]);
-      tcgen05_wait_ld();
-
-      const bool need_mask = (k0 + kBlockN > prm.Sk) || (prm.causal && k0 + kBlockN - 1 > q0);
-      float mx = -INFINITY;
-      if (need_mask) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 4; ++c) tmem_ld_wait(sr[c]);
+#endif
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+#if FO_WS_PIPE_LD == 1
+        if (c + 1 < 4) tmem_ld32(tS + (c + 1) * 32, sr[c + 1]);
+#endif
+        if (need_mask) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const int col = k0 + c * 32 + i;
-            float v = __uint_as_float(sr[c][i]);
-            if (col >= prm.Sk || (prm.causal && col > row)) v = -INFINITY;
-            sr[c][i] = __float_as_uint(v);
-            mx = fmaxf(mx, v);
+            if (col >= prm.Sk || (prm.causal && col > row)) sr[c][i] = 0xff800000u;  // -inf
           }
         }
-      } else {
+        // four independent accumulators (and 3-input max) keep the dependency chain short
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sr[c][i]));
+        for (int i = 0; i < 32; i += 8) {
+#if FO_WS_MAX3
+          mxa = max3(mxa, __uint_as_float(sr[c][i + 0]), __uint_as_float(sr[c][i + 1]));
+          mxb = max3(mxb, __uint_as_float(sr[c][i + 2]), __uint_as_float(sr[c][i + 3]));
+          mxc = max3(mxc, __uint_as_float(sr[c][i + 4]), __uint_as_float(sr[c][i + 5]));
+          mxd = max3(mxd, __uint_as_float(sr[c][i + 6]), __uint_as_float(sr[c][i + 7]));
+#else
+          mxa = fmaxf(mxa, fmaxf(__uint_as_float(sr[c][i + 0]), __uint_as_float(sr[c][i + 1])));
+          mxb = fmaxf(mxb, fmaxf(__uint_as_float(sr[c][i + 2]), __uint_as_float(sr[c][i + 3])));
+          mxc = fmaxf(mxc, fmaxf(__uint_as_float(sr[c][i + 4]), __uint_as_float(sr[c][i + 5])));
+          mxd = fmaxf(mxd, fmaxf(__uint_as_float(sr[c][i + 6]), __uint_as_float(sr[c][i + 7])));
+#endif
         }
+#if FO_WS_PIPE_LD == 1
+        if (c + 1 < 4) tmem_ld_wait(sr[c + 1]);
+#elif FO_WS_PIPE_LD == 2
+        if (c == 1) {
+          tmem_ld_wait(sr[2]);
+          tmem_ld_wait(sr[3]);
+        }
+#endif
       }
+      const float mx = fmaxf(fmaxf(mxa, mxb), fmaxf(mxc, mxd));
+      if ((warp & 3) == 0) trace_event(prm, s, j, 5);
       const float m_cand = fmaxf(m_run, mx * prm.scale_log2);
       const float m_new = (m_cand - m_run > kRescaleThreshold) ? m_cand : m_run;
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
       const float alpha = (m_new == m_run) ? 1.f : fast_exp2(m_run - m_use);
-      alpha_slot[(j & 1) * 128] = alpha;
-      mbar_arrive(bar_corr + s);
-
-      float rsum = 0.f;
-      uint32_t pr[2][32];
+      // P = exp2(S * scale - m), written to tensor memory in kPPieces pieces.  Of every eight
+      // column pairs, kEmuPairs are exponentiated with a polynomial on the FMA pipe instead of
+      // ex2 on the special-function unit (16 lanes per clock per SM), which would otherwise
+      // bound this loop; tiles that carry a mask use ex2 throughout so masked entries are 0.
+      const float2 sc2 = make_float2(prm.scale_log2, prm.scale_log2);
+      const float2 nm2 = make_float2(-m_use, -m_use);
+      float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
+      constexpr int kChunksPerPiece = 4 / kPPieces;  // 32-column chunks of S per piece
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int piece = 0; piece < kPPieces; ++piece) {
+        uint32_t pr[16 * kChunksPerPiece];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c][i]), prm.scale_log2, -m_use));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c][i + 1]), prm.scale_log2, -m_use));
-          rsum += p0 + p1;
-          pr[c >> 1][(c & 1) * 16 + (i >> 1)] = pack2<kBf16>(p0, p1);
+        for (int cc = 0; cc < kChunksPerPiece; ++cc) {
+          const int c = piece * kChunksPerPiece + cc;
+#pragma unroll
+          for (int q = 0; q < 16; ++q) {  // column pair q of the chunk
+            float2 x = __ffma2_rn(make_float2(__uint_as_float(sr[c][2 * q]), __uint_as_float(sr[c][2 * q + 1])), sc2, nm2);
+#if FO_WS_P_F16
+            // Round the exponent to fp16 and exponentiate both halves with one special-function
+            // instruction.  The row sum is taken in fp32 over these values; for fp16 inputs the
+            // packed result is P itself, for bf16 inputs it is re-rounded to bf16 (the MMA rejects
+            // an fp16 A operand next to a bf16 B operand: tried once, illegal instruction).
+            const uint32_t ph = exp2_f16x2(pack2<false>(x.x, x.y));
+            const float2 pf = __half22float2(*reinterpret_cast<const __half2*>(&ph));
+            if (q & 1) acc1 = __fadd2_rn(acc1, pf); else acc0 = __fadd2_rn(acc0, pf);
+            if constexpr (kBf16) pr[cc * 16 + q] = pack2<true>(pf.x, pf.y); else pr[cc * 16 + q] = ph;
+            continue;
+#endif
+            if ((q & 7) >= 8 - kEmuPairs && !need_mask) {
+              x = exp2_poly2(x);
+            } else {
+              x.x = fast_exp2(x.x);
+              x.y = fast_exp2(x.y);
+            }
+            if (q & 1) acc1 = __fadd2_rn(acc1, x); else acc0 = __fadd2_rn(acc0, x);
+            pr[cc * 16 + q] = pack2<kBf16>(x.x, x.y);
+          }
+          if (c == 0) {
+            // hand the rescale factor to the correction warps once the first exponentials are
+            // in flight (it is off this thread's critical path)
+            alpha_slot[(j & 1) * 128] = alpha;
+            mbar_arrive(bar_corr + s);
+            if ((warp & 3) == 0) trace_event(prm, s, j, 1);
+          }
         }
+        if ((warp & 3) == 0 && piece == kPPieces - 1) trace_event(prm, s, j, 2);
+        // 16 packed columns per 32-column chunk of S
+#pragma unroll
+        for (int cc = 0; cc < kChunksPerPiece; ++cc)
+          tmem_st16(tS + (piece * kChunksPerPiece + cc) * 16, pr + cc * 16);
+        tcgen05_wait_st();
+        tcgen05_fence_before_sync();
+        mbar_arrive(bar_p_full + kMaxPPieces * s + piece);
+        if ((warp & 3) == 0 && piece == kPPieces - 1) trace_event(prm, s, j, 3);
       }
-      tmem_st32(tS, pr[0]);
-      tmem_st32(tS + 32, pr[1]);
-      tcgen05_wait_st();
-      tcgen05_fence_before_sync();
-      mbar_arrive(bar_p_full + s);
+      const float rsum = (acc0.x + acc0.y) + (acc1.x + acc1.y);
       l_run = l_run * alpha + rsum;
       m_run = m_new;
     }
@@ -227,7 +323,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             for (int c = 0; c < D / 32; ++c) {
               uint32_t orr[32];
               tmem_ld32(tO + c * 32, orr);
-              tcgen05_wait_ld();
+              tmem_ld_wait(orr);
 #pragma unroll
               for (int i = 0; i < 32; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
               tmem_st32(tO + c * 32, orr);
@@ -258,7 +354,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       for (int c = 0; c < D / 32; ++c) {
         uint32_t orr[32];
         tmem_ld32(tO + c * 32, orr);
-        tcgen05_wait_ld();
+        tmem_ld_wait(orr);
         if (row_ok) {
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
@@ -282,36 +378,59 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       // ================================ MMA issuer ================================
       constexpr uint32_t idesc_qk = make_idesc(kBf16, kBlockM, kBlockN, 0, 0);
       constexpr uint32_t idesc_pv = make_idesc(kBf16, kBlockM, D, 0, 1);
-      const uint32_t aQ = smem_u32(sQ);
-      const uint32_t aKV = smem_u32(sKV);
-      const bool issuer = lane == 0;
-
+      // Everything below is warp-uniform; only the tcgen05 instructions themselves are issued by
+      // one elected lane.  Descriptors are kept as 32-bit low halves: per instruction one add.
+      const uint32_t q_lo0 = desc_lo(smem_u32(sQ), 16);
+      const uint32_t q_lo1 = desc_lo(smem_u32(sQ) + kTileBytes, 16);
+      const uint32_t kv_k_lo = desc_lo(smem_u32(sKV), 16);         // K tiles: K-major
+      const uint32_t kv_v_lo = desc_lo(smem_u32(sKV), kBoxBytes);  // V tiles: N-major
+      constexpr uint32_t kStageStep = kTileBytes >> 4;
+      const uint32_t tS0 = tmem_base + Cfg::kColS0;
+      const uint32_t tO0 = tmem_base + Cfg::kColO0;
+      // S_s = Q_s K^T over the K tile in ring slot `stage`
       auto issue_s = [&](int s, int stage) {
-        const uint32_t tS = tmem_base + Cfg::kColS0 + s * kBlockN;
+        const uint32_t a_lo = s ? q_lo1 : q_lo0;
+        const uint32_t b_lo = kv_k_lo + stage * kStageStep;
+        const uint32_t tS = tS0 + s * kBlockN;
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk)
-          umma_ss(tS, kmajor_desc(aQ + s * kTileBytes, kk), kmajor_desc(aKV + stage * kTileBytes, kk), idesc_qk,
-                  kk > 0 ? 1u : 0u);
+        for (int kk = 0; kk < D / 16; ++kk) {
+          // k-slice kk: box kk/4, 32 bytes per slice inside the 128-byte swizzle span
+          constexpr uint32_t kBoxStep = kBoxBytes >> 4;
+          const uint32_t off = (kk >> 2) * kBoxStep + (kk & 3) * 2;
+          umma_ss_lo_elect(tS, a_lo + off, b_lo + off, idesc_qk, kk > 0 ? 1u : 0u);
+        }
       };
-      auto issue_pv = [&](int s, int stage, bool acc) {
-        const uint32_t tP = tmem_base + Cfg::kColS0 + s * kBlockN;
-        const uint32_t tO = tmem_base + Cfg::kColO0 + s * D;
+      // PV over one piece of the tile's keys: k-slices piece*8/kPPieces ...
+      auto issue_pv_piece = [&](int s, int stage, int piece, bool acc) {
+        const uint32_t tP = tS0 + s * kBlockN;
+        const uint32_t tO = tO0 + s * D;
+        const uint32_t b_lo = kv_v_lo + stage * kStageStep;
 #pragma unroll
-        for (int kk = 0; kk < kBlockN / 16; ++kk)
-          umma_ts(tO, tP + kk * 8, nmajor_desc(aKV + stage * kTileBytes, kk), idesc_pv, (acc || kk > 0) ? 1u : 0u);
+        for (int k4 = 0; k4 < 8 / kPPieces; ++k4) {
+          const int kk = piece * (8 / kPPieces) + k4;
+          // 16 key rows per slice: 2048 bytes of V, 8 packed columns of P
+          umma_ts_lo_elect(tO, tP + kk * 8, b_lo + kk * 128, idesc_pv, (acc || kk > 0) ? 1u : 0u);
+        }
+      };
+      // waits for each piece of P_s of key tile j and issues its MMAs; the caller commits
+      auto pv_tile = [&](int s, int stage, int j) {
+        mbar_wait(bar_o_scaled + s, j & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_SOFTMAX);
+#pragma unroll
+        for (int piece = 0; piece < kPPieces; ++piece) {
+          mbar_wait(bar_p_full + kMaxPPieces * s + piece, j & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_SOFTMAX);
+          tcgen05_fence_after_sync();
+          issue_pv_piece(s, stage, piece, j > 0);
+        }
       };
 
       mbar_wait(bar_q_full, 0, cta_abort, dstat, FO_STATUS_TIMEOUT_TMA);
       mbar_wait(bar_kv_full + 0, 0, cta_abort, dstat, FO_STATUS_TIMEOUT_TMA);  // K_0 is ring slot 0
       tcgen05_fence_after_sync();
-      if (issuer) {
-        issue_s(0, 0);
-        tcgen05_commit(bar_s_full + 0);
-        issue_s(1, 0);
-        tcgen05_commit(bar_s_full + 1);
-        tcgen05_commit(bar_kv_empty + 0);
-      }
-      __syncwarp();
+      issue_s(0, 0);
+      tcgen05_commit_elect(bar_s_full + 0);
+      issue_s(1, 0);
+      tcgen05_commit_elect(bar_s_full + 1);
+      tcgen05_commit_elect(bar_kv_empty + 0);
       for (int j = 0; j < n1; ++j) {
         const int iv = 2 * j + 1;  // ring index of V_j; K_{j+1} is iv + 1
         const int st_v = iv % kStages;
@@ -319,34 +438,26 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         const bool more = j + 1 < n1;
         mbar_wait(bar_kv_full + st_v, (iv / kStages) & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_TMA);
         if (more) mbar_wait(bar_kv_full + st_k, ((iv + 1) / kStages) & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_TMA);
+        trace_event(prm, 2, j, 0);
         if (j < n0) {
-          mbar_wait(bar_p_full + 0, j & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_SOFTMAX);
-          mbar_wait(bar_o_scaled + 0, j & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_SOFTMAX);
-          tcgen05_fence_after_sync();
-          if (issuer) {
-            issue_pv(0, st_v, j > 0);
-            tcgen05_commit(bar_o_full + 0);
-            if (j + 1 < n0) {
-              issue_s(0, st_k);
-              tcgen05_commit(bar_s_full + 0);
-            }
-          }
-          __syncwarp();
-        }
-        mbar_wait(bar_p_full + 1, j & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_SOFTMAX);
-        mbar_wait(bar_o_scaled + 1, j & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_SOFTMAX);
-        tcgen05_fence_after_sync();
-        if (issuer) {
-          issue_pv(1, st_v, j > 0);
-          tcgen05_commit(bar_o_full + 1);
-          tcgen05_commit(bar_kv_empty + st_v);
-          if (more) {
-            issue_s(1, st_k);
-            tcgen05_commit(bar_s_full + 1);
-            tcgen05_commit(bar_kv_empty + st_k);
+          pv_tile(0, st_v, j);
+          trace_event(prm, 2, j, 1);
+          tcgen05_commit_elect(bar_o_full + 0);
+          if (j + 1 < n0) {
+            issue_s(0, st_k);
+            tcgen05_commit_elect(bar_s_full + 0);
           }
         }
-        __syncwarp();
+        trace_event(prm, 2, j, 2);
+        pv_tile(1, st_v, j);
+        trace_event(prm, 2, j, 3);
+        tcgen05_commit_elect(bar_o_full + 1);
+        tcgen05_commit_elect(bar_kv_empty + st_v);
+        if (more) {
+          issue_s(1, st_k);
+          tcgen05_commit_elect(bar_s_full + 1);
+          tcgen05_commit_elect(bar_kv_empty + st_k);
+        }
       }
     } else if (warp == 13) {
       // ================================ TMA producer ================================

@@ -160,6 +160,15 @@ int64_t fo_launch_count(void);
 int fo_debug_umma_tile(const void* a, const void* b, float* c, int N, int K,
                        int dtype, int mode, int device, void* stream);
 
+/*
+ * Kernel-tuning aid: after fo_debug_set_attn_trace(buf) the warp-specialised attention kernel
+ * records, for its first CTA, SM clock values of the hand-offs between its softmax warps and its
+ * MMA issuer into `buf` (device memory of roles*iters*events 64-bit words, see
+ * fo_debug_attn_trace_shape; zero it first).  Pass NULL to switch the recording off.
+ */
+int fo_debug_set_attn_trace(void* device_buffer);
+int fo_debug_attn_trace_shape(int* roles, int* iters, int* events);
+
 #ifdef __cplusplus
 }
 #endif
