@@ -62,7 +62,7 @@ class ClockSampler:
         0x80: "hw_power_brake_slowdown",
     }
 
-    def __init__(self, index: int, period_s: float = 0.02):
+    def __init__(self, index: int, period_s: float = 0.005):
         self.index, self.period = index, period_s
         self.samples, self.reasons = [], set()
         self.max_mhz = None
@@ -388,6 +388,30 @@ def bench_lion_c5(d: Dist, steps: int, warmup: int, peaks):
         recv = (d.world - 1) / d.world * total * 2
         res["all_gather"] = {"ms": ms_gather, "bus_gbs": recv / (ms_gather * 1e-3) / 1e9,
                              "bytes_received_per_gpu": recv}
+        # the same step with the distribution fused into the kernel: peer stores over NVLink into a
+        # symmetric-memory flat buffer, ranks ordered by device-side barriers before and after
+        try:
+            import torch.distributed._symmetric_memory as symm_mem
+            from fast_ops_b200.lion.lion_optimizer import _flat_step_push
+
+            sym_p = symm_mem.empty(total, dtype=torch.bfloat16, device=d.device)
+            sym_p.copy_(flat_p)
+            del flat_p
+            flat_p = sym_p
+            hdl = symm_mem.rendezvous(sym_p, d.dist.group.WORLD)
+            peers = [int(ptr) for r, ptr in enumerate(hdl.buffer_ptrs) if r != d.rank]
+
+            def fused_step():
+                hdl.barrier(channel=0)
+                _flat_step_push(sym_p, flat_g, m_shard, begin, end, peers, 3e-5, (0.9, 0.99), 0.1)
+                hdl.barrier(channel=1)
+
+            ms_fused, _ = timed_steps(d, fused_step, steps, warmup)
+            res["fused_gather"] = {"ms_per_step": ms_fused, "value": n * 10 / (ms_fused * 1e-3) / 1e9, "unit": "GB/s",
+                                   "nvlink_egress_gbs_per_gpu": recv / (ms_fused * 1e-3) / 1e9,
+                                   "speedup_vs_step_plus_all_gather": ms_full / ms_fused}
+        except Exception as exc:  # symmetric memory unavailable: report, keep the NCCL numbers
+            res["fused_gather"] = {"unavailable": repr(exc)[:200]}
     del flat_p, flat_g, m_shard
     torch.cuda.empty_cache()
     return res

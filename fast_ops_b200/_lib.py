@@ -42,6 +42,9 @@ SIGNATURES = {
                                                      _c.c_int, _PTR]),
     "fo_lion_flat_step": (_c.c_int, [_PTR, _PTR, _PTR, _c.c_int64, _c.c_int64, _c.c_int, _c.c_int, _c.c_int,
                                      _c.c_double, _c.c_double, _c.c_double, _c.c_double, _c.c_int, _PTR]),
+    "fo_lion_flat_step_push": (_c.c_int, [_PTR, _PTR, _PTR, _c.c_int64, _c.c_int64, _c.POINTER(_PTR), _c.c_int,
+                                          _c.c_int, _c.c_int, _c.c_int,
+                                          _c.c_double, _c.c_double, _c.c_double, _c.c_double, _c.c_int, _PTR]),
     "fo_lion_clear_cache": (_c.c_int, []),
     "fo_launch_count": (_c.c_int64, []),
     "fo_debug_set_attn_trace": (_c.c_int, [_PTR]),

@@ -497,3 +497,135 @@ extern "C" int fo_lion_multi_tensor_step_noalloc(void* const* params, const void
   plan.d_blob = d_table;
   return launch(plan, p_dtype, m_dtype, c, s);
 }
+
+// ---- ZeRO-1 step fused with the distribution of the updated weights ---------------------------
+//
+// The sharded step is followed by an all-gather of the updated parameters.  Here the kernel that
+// computes a rank's slice also stores every updated 16-byte vector into the same position of
+// each peer's flat parameter buffer (plain stores to peer memory over NVLink), so the transfer
+// overlaps the HBM-bound update instead of following it.  The caller provides the peers' base
+// pointers (the buffers must be mapped for peer access, e.g. a symmetric-memory allocation) and
+// orders the ranks around the call: no peer may still read its buffer when the stores begin, and
+// every rank must have finished before any of them reads the gathered weights.
+
+namespace {
+
+constexpr int kMaxPeers = 7;  // the other GPUs of one 8-GPU NVSwitch domain
+
+struct PeerList {
+  void* base[kMaxPeers];
+  int n;
+};
+
+template <typename TP, typename TM>
+__global__ void __launch_bounds__(kThreads)
+lion_flat_push_kernel(TP* __restrict__ p_local, const TP* __restrict__ g, TM* __restrict__ m_shard,
+                      int64_t begin, int64_t numel, PeerList peers, LionConsts c) {
+  // p_local, g and the peers' bases address element 0 of the flat buffers; m_shard addresses the
+  // momentum of element `begin`.
+  const int64_t total_chunks = (numel + kChunk - 1) / kChunk;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(p_local + begin) | reinterpret_cast<uintptr_t>(g + begin) |
+                         reinterpret_cast<uintptr_t>(m_shard)) & 15) == 0;
+  for (int64_t chunk = blockIdx.x; chunk < total_chunks; chunk += gridDim.x) {
+    const int64_t base = chunk * kChunk;
+    const int64_t remaining = numel - base;
+    TP* p = p_local + begin + base;
+    const TP* gg = g + begin + base;
+    TM* m = m_shard + base;
+    if (aligned && remaining >= kChunk) {
+      Group<TP> pv[kUnroll], gv[kUnroll];
+      Group<TM> mv[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const int off = (u * kThreads + threadIdx.x) * kVec;
+        load_group(pv[u], p + off);
+        load_group(gv[u], gg + off);
+        load_group(mv[u], m + off);
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+#pragma unroll
+        for (int i = 0; i < kVec; ++i) lion_element<TP, TM>(pv[u].v[i], gv[u].v[i], mv[u].v[i], c);
+        const int off = (u * kThreads + threadIdx.x) * kVec;
+        store_group(p + off, pv[u]);
+        store_group(m + off, mv[u]);
+#pragma unroll
+        for (int r = 0; r < kMaxPeers; ++r) {
+          if (r < peers.n) {
+            TP* dst = static_cast<TP*>(peers.base[r]) + begin + base + off;
+            constexpr int n16 = sizeof(TP) * kVec / 16;
+#pragma unroll
+            for (int q = 0; q < n16; ++q)
+              reinterpret_cast<uint4*>(dst)[q] = reinterpret_cast<const uint4*>(pv[u].v)[q];
+          }
+        }
+      }
+    } else {
+      const int n = remaining < kChunk ? static_cast<int>(remaining) : kChunk;
+      for (int i = threadIdx.x; i < n; i += kThreads) {
+        TP pe = p[i];
+        TM me = m[i];
+        lion_element<TP, TM>(pe, gg[i], me, c);
+        p[i] = pe;
+        m[i] = me;
+#pragma unroll
+        for (int r = 0; r < kMaxPeers; ++r)
+          if (r < peers.n) static_cast<TP*>(peers.base[r])[begin + base + i] = pe;
+      }
+    }
+  }
+}
+
+template <typename TP, typename TM>
+int launch_push(void* p, const void* g, void* m, int64_t begin, int64_t numel, const PeerList& peers,
+                const LionConsts& c, int device, cudaStream_t stream) {
+  const int64_t total_chunks = (numel + kChunk - 1) / kChunk;
+  int64_t grid = static_cast<int64_t>(sm_count(device)) * 8;
+  if (grid > total_chunks) grid = total_chunks;
+  lion_flat_push_kernel<TP, TM><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
+      static_cast<TP*>(p), static_cast<const TP*>(g), static_cast<TM*>(m), begin, numel, peers, c);
+  fo::g_launch_count.fetch_add(1, std::memory_order_relaxed);
+  FO_CUDA_CHECK(cudaGetLastError());
+  return FO_OK;
+}
+
+}  // namespace
+
+extern "C" int fo_lion_flat_step_push(void* param, const void* grad, void* exp_avg_shard,
+                                      int64_t begin, int64_t end,
+                                      void* const* peer_params, int n_peers,
+                                      int p_dtype, int g_dtype, int m_dtype,
+                                      double lr, double beta1, double beta2, double weight_decay,
+                                      int device, void* stream) {
+  fo::clear_error();
+  if (int rc = check_dtypes(p_dtype, g_dtype, m_dtype)) return rc;
+  FO_REQUIRE(begin >= 0 && end >= begin, "bad shard range [%lld, %lld)", (long long)begin, (long long)end);
+  FO_REQUIRE(n_peers >= 0 && n_peers <= kMaxPeers, "n_peers must be in [0, %d] (got %d)", kMaxPeers, n_peers);
+  FO_REQUIRE(n_peers == 0 || peer_params != nullptr, "null peer list");
+  if (end == begin) return FO_OK;
+  FO_REQUIRE(param && grad && exp_avg_shard, "null pointer");
+  PeerList peers;
+  peers.n = n_peers;
+  for (int i = 0; i < kMaxPeers; ++i) peers.base[i] = nullptr;
+  for (int i = 0; i < n_peers; ++i) {
+    FO_REQUIRE(peer_params[i] != nullptr, "peer %d has a null buffer", i);
+    FO_REQUIRE(peer_params[i] != param, "peer %d is the local buffer", i);
+    peers.base[i] = peer_params[i];
+  }
+  LionConsts c;
+  if (int rc = make_consts(lr, beta1, beta2, weight_decay, p_dtype, m_dtype, &c)) return rc;
+  fo::DeviceGuard guard(device);
+  FO_REQUIRE(guard.ok, "cannot make device %d current", device);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int64_t n = end - begin;
+#define FO_LION_PUSH_CASE(PD, MD, TP, TM) \
+  if (p_dtype == PD && m_dtype == MD) return launch_push<TP, TM>(param, grad, exp_avg_shard, begin, n, peers, c, device, s);
+  FO_LION_PUSH_CASE(FO_BF16, FO_BF16, __nv_bfloat16, __nv_bfloat16)
+  FO_LION_PUSH_CASE(FO_BF16, FO_F32, __nv_bfloat16, float)
+  FO_LION_PUSH_CASE(FO_F16, FO_F16, __half, __half)
+  FO_LION_PUSH_CASE(FO_F16, FO_F32, __half, float)
+  FO_LION_PUSH_CASE(FO_F32, FO_F32, float, float)
+  FO_LION_PUSH_CASE(FO_F32, FO_BF16, float, __nv_bfloat16)
+#undef FO_LION_PUSH_CASE
+  return fo::fail(FO_ERR_UNSUPPORTED, "no fused-gather Lion kernel for dtypes p=%d m=%d", p_dtype, m_dtype);
+}

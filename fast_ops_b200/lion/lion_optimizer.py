@@ -13,6 +13,9 @@ Keyword-only extensions:
   process_group    a torch.distributed group: parameters are laid out in one flat buffer, each
                    rank updates only its 1/world_size slice (and keeps momentum only for it),
                    then ONE all-gather distributes the updated weights (ZeRO-1).
+  fused_gather     with process_group: the flat parameter buffer is a symmetric-memory
+                   allocation and the step kernel itself stores the updated slice into every
+                   peer's buffer over NVLink, replacing the all-gather.
 """
 from __future__ import annotations
 
@@ -71,6 +74,20 @@ def _check_triple(param: Tensor, grad: Tensor, exp_avg: Tensor) -> None:
         raise RuntimeError("param and grad must share a memory layout")
 
 
+def _flat_step_push(p: Tensor, g: Tensor, m_shard: Tensor, begin: int, end: int, peer_ptrs, lr: float, betas,
+                    wd: float) -> None:
+    """Lion step on [begin, end) that also stores the result into the peers' flat buffers
+    (C-ABI fo_lion_flat_step_push).  `peer_ptrs`: device addresses of the peers' element 0."""
+    lib = _lib.load()
+    n = len(peer_ptrs)
+    arr = (ctypes.c_void_p * max(n, 1))(*peer_ptrs)
+    _lib.check(lib.fo_lion_flat_step_push(
+        p.data_ptr(), g.data_ptr(), m_shard.data_ptr(), begin, end, arr, n,
+        _lib.dtype_code(p.dtype), _lib.dtype_code(g.dtype), _lib.dtype_code(m_shard.dtype),
+        float(lr), float(betas[0]), float(betas[1]), float(wd), p.device.index,
+        _lib.current_stream_ptr(p.device)))
+
+
 def _flat_step(p: Tensor, g: Tensor, m_shard: Tensor, begin: int, end: int, lr: float, betas, wd: float) -> None:
     """Lion step on elements [begin, end) of the flat buffers (C-ABI fo_lion_flat_step)."""
     lib = _lib.load()
@@ -99,7 +116,7 @@ class Lion(Optimizer):
 
     def __init__(self, params: Iterable, lr: float = 1e-4, betas: Tuple[float, float] = (0.9, 0.99),
                  weight_decay: float = 0.0, *, momentum_dtype: Optional[torch.dtype] = None,
-                 process_group=None) -> None:
+                 process_group=None, fused_gather: bool = False) -> None:
         if lr <= 0:
             raise RuntimeError(f"expected positive LR, got {lr}")
         if not all(0 <= beta <= 1 for beta in betas):
@@ -112,8 +129,10 @@ class Lion(Optimizer):
         self._lists: Dict[tuple, _TensorList] = {}
         self._pg = process_group
         self._zero = None
+        if fused_gather and process_group is None:
+            raise RuntimeError("fused_gather needs a process_group")
         if process_group is not None:
-            self._zero = _Zero1State(self, process_group, momentum_dtype)
+            self._zero = _Zero1State(self, process_group, momentum_dtype, fused_gather)
 
     # -- multi-tensor path ---------------------------------------------------------------
     @torch.no_grad()
@@ -177,7 +196,7 @@ class _Zero1State:
     the all-gather of updated weights.
     """
 
-    def __init__(self, opt: Lion, group, momentum_dtype: Optional[torch.dtype]):
+    def __init__(self, opt: Lion, group, momentum_dtype: Optional[torch.dtype], fused_gather: bool = False):
         import torch.distributed as dist
 
         self.opt = opt
@@ -195,7 +214,19 @@ class _Zero1State:
                 raise RuntimeError("process_group mode needs all parameters on one device with one dtype")
         self.params = params
         self.layout = FlatLayout.build([p.numel() for p in params], self.world)
-        self.flat_p = torch.zeros(self.layout.total, dtype=dtype, device=device)
+        self.symm = None
+        self.peer_ptrs: List[int] = []
+        if fused_gather and self.world > 1:
+            # peer-mapped allocation: every rank can store into every other rank's buffer
+            import torch.distributed._symmetric_memory as symm_mem
+
+            self.flat_p = symm_mem.empty(self.layout.total, dtype=dtype, device=device)
+            self.flat_p.zero_()
+            self.symm = symm_mem.rendezvous(self.flat_p, group)
+            ptrs = list(self.symm.buffer_ptrs)
+            self.peer_ptrs = [int(ptrs[r]) for r in range(self.world) if r != self.rank]
+        else:
+            self.flat_p = torch.zeros(self.layout.total, dtype=dtype, device=device)
         self.flat_g = torch.zeros(self.layout.total, dtype=dtype, device=device)
         self._grad_views: List[Tensor] = []
         with torch.no_grad():
@@ -228,6 +259,14 @@ class _Zero1State:
                 gview.copy_(p.grad)
                 p.grad = gview
         group = self.opt.param_groups[0]
+        if self.symm is not None:
+            # ranks meet before any of them overwrites a peer's weights, and again before any of
+            # them reads the gathered result (device-side barriers on the current stream)
+            self.symm.barrier(channel=0)
+            _flat_step_push(self.flat_p, self.flat_g, self.m_shard, self.begin, self.end, self.peer_ptrs,
+                            group["lr"], group["betas"], group["weight_decay"])
+            self.symm.barrier(channel=1)
+            return
         self.flat_step_fn(self.flat_p, self.flat_g, self.m_shard, self.begin, self.end, group["lr"],
                           group["betas"], group["weight_decay"])
         if self.world > 1:

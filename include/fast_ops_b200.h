@@ -118,6 +118,22 @@ int fo_lion_flat_step(void* param, const void* grad, void* exp_avg_shard,
                       int device, void* stream);
 
 /*
+ * fo_lion_flat_step fused with the distribution of the updated weights: every updated value of
+ * [begin, end) is stored to the local flat buffer and, by plain stores over NVLink, to the same
+ * position of each peer's flat buffer (`peer_params`: HOST array of n_peers <= 7 device pointers
+ * to element 0 of the peers' buffers, mapped for peer access).  It replaces "step, then
+ * all-gather" of a ZeRO-1 optimizer step; the reference has neither.  The caller orders the ranks:
+ * no peer may still be reading its buffer when this kernel starts, and all ranks' kernels must
+ * have finished before any rank reads the gathered weights.
+ */
+int fo_lion_flat_step_push(void* param, const void* grad, void* exp_avg_shard,
+                           int64_t begin, int64_t end,
+                           void* const* peer_params, int n_peers,
+                           int p_dtype, int g_dtype, int m_dtype,
+                           double lr, double beta1, double beta2, double weight_decay,
+                           int device, void* stream);
+
+/*
  * fo_lion_multi_tensor_step for callers that must not allocate: same arguments, same kernel,
  * same results, but the device-side tensor table lives in a fixed array inside the library
  * (about 40 KiB per device that loads the library, held until the process exits) instead of
