@@ -26,13 +26,15 @@ def _strides3(t: Tensor):
 
 def flash_attention_forward(Q: Tensor, K: Tensor, V: Tensor, *, causal: bool = False,
                             softmax_scale: Optional[float] = None,
-                            return_lse: bool = False) -> Union[Tensor, Tuple[Tensor, Tensor]]:
+                            return_lse: bool = False,
+                            out: Optional[Tensor] = None) -> Union[Tensor, Tuple[Tensor, Tensor]]:
     """O = softmax(scale * Q K^T [+ causal mask]) V on the CUDA device holding Q.
 
     Q: (B, H, M, D); K, V: (B, H, N, D); fp16 or bf16; D in {64, 128}; the last dimension
     contiguous, the others with strides that are multiples of 8 elements (so (B, S, H, D)
     tensors viewed as (B, H, S, D) are accepted without a copy).  Returns O (B, H, M, D) in
-    Q's dtype, plus LSE (B, H, M) fp32 when `return_lse`.
+    Q's dtype, plus LSE (B, H, M) fp32 when `return_lse`.  `out`, if given, receives O: shape
+    (B, H, M, D), Q's dtype and device, last dimension contiguous (any layout otherwise).
     """
     if not (isinstance(Q, Tensor) and isinstance(K, Tensor) and isinstance(V, Tensor)):
         raise RuntimeError("Q, K, V must be tensors")
@@ -57,7 +59,12 @@ def flash_attention_forward(Q: Tensor, K: Tensor, V: Tensor, *, causal: bool = F
             raise RuntimeError(f"{name}: the last dimension must be contiguous")
     scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(D)
 
-    O = torch.empty((B, H, M, D), dtype=Q.dtype, device=Q.device)
+    if out is None:
+        O = torch.empty((B, H, M, D), dtype=Q.dtype, device=Q.device)
+    else:
+        if out.shape != (B, H, M, D) or out.dtype != Q.dtype or out.device != Q.device or out.stride(3) != 1:
+            raise RuntimeError("out must be (B, H, M, D) with Q's dtype and device and a contiguous last dimension")
+        O = out
     lse = torch.empty((B, H, M), dtype=torch.float32, device=Q.device) if return_lse else None
     lib = _lib.load()
     rc = lib.fo_flash_attn_fwd(

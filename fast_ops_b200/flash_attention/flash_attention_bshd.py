@@ -20,6 +20,9 @@ def flash_attn_bshd(q: Tensor, k: Tensor, v: Tensor, bias: Optional[Tensor] = No
         raise RuntimeError("attention bias is not implemented in fast_ops_b200")
     if dropout_p != 0.0:
         raise RuntimeError("attention dropout is not implemented in fast_ops_b200")
-    out = flash_attention_forward(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), causal=causal,
-                                  softmax_scale=softmax_scale)
-    return out.transpose(1, 2)
+    import torch
+
+    o = torch.empty_like(q)  # the reference allocates O with q's layout (flash_attention_triton.py:773)
+    flash_attention_forward(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), causal=causal,
+                            softmax_scale=softmax_scale, out=o.transpose(1, 2))
+    return o

@@ -143,3 +143,20 @@ def test_reference_call_signature_and_errors(cuda_device):
     with pytest.raises(RuntimeError):
         bad = torch.randn(1, 2, 256, 136, device=cuda_device).half()
         multi_head_attention(bad, bad, bad)  # head_dim > 128
+
+
+def test_host_pipelined_forward_matches_device_forward(cuda_device):
+    from fast_ops_b200.flash_attention import flash_attention_forward_host
+
+    q, k, v = attention_inputs(21, 2, 6, 512, 512, 64, torch.bfloat16)
+    hq, hk, hv = (t.pin_memory() for t in (q, k, v))
+    host_out = flash_attention_forward_host(hq, hk, hv, device=cuda_device, causal=True, heads_per_chunk=4)
+    torch.cuda.synchronize()
+    dev_out = flash_attention_forward(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device), causal=True)
+    assert host_out.device.type == "cpu" and torch.equal(host_out, dev_out.cpu())
+    # a second call reuses the workspace and the slots in a different order of completion
+    host_out2 = flash_attention_forward_host(hq, hk, hv, device=cuda_device, causal=True, heads_per_chunk=1)
+    torch.cuda.synchronize()
+    assert torch.equal(host_out2, host_out)
+    with pytest.raises(RuntimeError):
+        flash_attention_forward_host(q.to(cuda_device), hk, hv)
