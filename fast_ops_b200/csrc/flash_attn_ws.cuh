@@ -23,26 +23,10 @@
 
 namespace fo {
 
-// Tuning switches of the softmax warps (compile-time; the defaults are the measured best).
+// 1: overlap each tensor-memory load of S with the row maximum of the previous chunk.
 #ifndef FO_WS_PIPE_LD
-#define FO_WS_PIPE_LD 1  // 1: overlap each tensor-memory load with the row max of the previous chunk
+#define FO_WS_PIPE_LD 1
 #endif
-#ifndef FO_WS_MAX3
-#define FO_WS_MAX3 1  // 3-input max
-#endif
-#ifndef FO_WS_EMU_PAIRS
-#define FO_WS_EMU_PAIRS 0  // of every 8 column pairs, how many use the polynomial exp2 (0..8)
-#endif
-#ifndef FO_WS_P_F16
-#define FO_WS_P_F16 0  // 1: exponentials from the packed-half ex2 (two per instruction); 0: fp32 ex2
-#endif
-
-#ifndef FO_WS_P_PIECES
-#define FO_WS_P_PIECES 1  // pieces (1, 2 or 4) in which P is handed to the MMA issuer
-#endif
-constexpr int kPPieces = FO_WS_P_PIECES;
-constexpr int kEmuPairs = FO_WS_EMU_PAIRS;
-constexpr int kMaxPPieces = 4;
 
 template <int D>
 struct WsConfig {
@@ -54,7 +38,7 @@ struct WsConfig {
   static constexpr int kOffAlpha = kOffKV + kStages * kTileBytes;  // [2 tiles][2 buffers][128] float
   static constexpr int kOffFinal = kOffAlpha + 2 * 2 * 128 * 4;    // [2 tiles][l, m][128] float
   static constexpr int kOffBars = kOffFinal + 2 * 2 * 128 * 4;
-  static constexpr int kNumBars = 1 + 2 * kStages + 2 * 5 + 2 * kMaxPPieces;
+  static constexpr int kNumBars = 1 + 2 * kStages + 2 * 6;
   static constexpr int kOffMisc = kOffBars + kNumBars * 8;
   static constexpr int kSmemBytes = kOffMisc + 64 + 1024 /* alignment slack */;
   static constexpr uint32_t kTmemCols = 512;
@@ -97,8 +81,8 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   uint64_t* bar_kv_full = bars + 1;             // [kStages] TMA -> MMA
   uint64_t* bar_kv_empty = bar_kv_full + kStages;  // [kStages] MMA -> TMA
   uint64_t* bar_s_full = bar_kv_empty + kStages;   // [2] MMA -> softmax
-  uint64_t* bar_p_full = bar_s_full + 2;           // [2 tiles][kMaxPPieces] softmax -> MMA (128 arrivals)
-  uint64_t* bar_o_full = bar_p_full + 2 * kMaxPPieces;  // [2] MMA -> correction
+  uint64_t* bar_p_full = bar_s_full + 2;           // [2] softmax -> MMA (128 arrivals)
+  uint64_t* bar_o_full = bar_p_full + 2;           // [2] MMA -> correction
   uint64_t* bar_corr = bar_o_full + 2;             // [2] softmax -> correction (128 arrivals)
   uint64_t* bar_o_scaled = bar_corr + 2;           // [2] correction -> MMA (128 arrivals)
   // [2] softmax -> correction, once: final row sum and maximum are in shared memory.  A barrier
@@ -133,7 +117,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar_s_full + s, 1);
-      for (int i = 0; i < kMaxPPieces; ++i) mbar_init(bar_p_full + kMaxPPieces * s + i, 128);
+      mbar_init(bar_p_full + s, 128);
       mbar_init(bar_o_full + s, 1);
       mbar_init(bar_corr + s, 128);
       mbar_init(bar_o_scaled + s, 128);
@@ -178,16 +162,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       const bool need_mask = (k0 + kBlockN > prm.Sk) || (prm.causal && k0 + kBlockN - 1 > q0);
       uint32_t sr[4][32];
       float mxa = -INFINITY, mxb = -INFINITY, mxc = -INFINITY, mxd = -INFINITY;
-#if FO_WS_PIPE_LD == 2
-      // two loads in flight: chunks 0,1, then chunks 2,3 while 0,1 are reduced
-      tmem_ld32(tS, sr[0]);
-      tmem_ld32(tS + 32, sr[1]);
-      tmem_ld_wait(sr[0]);
-      tmem_ld_wait(sr[1]);
-      tmem_ld32(tS + 64, sr[2]);
-      tmem_ld32(tS + 96, sr[3]);
-      if ((warp & 3) == 0) trace_event(prm, s, j, 4);
-#elif FO_WS_PIPE_LD == 1
+#if FO_WS_PIPE_LD == 1
       // Tensor-memory loads are software-pipelined against the row maximum: chunk c+1 is in
       // flight while chunk c is reduced.
       tmem_ld32(tS, sr[0]);
@@ -214,25 +189,13 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         // four independent accumulators (and 3-input max) keep the dependency chain short
 #pragma unroll
         for (int i = 0; i < 32; i += 8) {
-#if FO_WS_MAX3
           mxa = max3(mxa, __uint_as_float(sr[c][i + 0]), __uint_as_float(sr[c][i + 1]));
           mxb = max3(mxb, __uint_as_float(sr[c][i + 2]), __uint_as_float(sr[c][i + 3]));
           mxc = max3(mxc, __uint_as_float(sr[c][i + 4]), __uint_as_float(sr[c][i + 5]));
           mxd = max3(mxd, __uint_as_float(sr[c][i + 6]), __uint_as_float(sr[c][i + 7]));
-#else
-          mxa = fmaxf(mxa, fmaxf(__uint_as_float(sr[c][i + 0]), __uint_as_float(sr[c][i + 1])));
-          mxb = fmaxf(mxb, fmaxf(__uint_as_float(sr[c][i + 2]), __uint_as_float(sr[c][i + 3])));
-          mxc = fmaxf(mxc, fmaxf(__uint_as_float(sr[c][i + 4]), __uint_as_float(sr[c][i + 5])));
-          mxd = fmaxf(mxd, fmaxf(__uint_as_float(sr[c][i + 6]), __uint_as_float(sr[c][i + 7])));
-#endif
         }
 #if FO_WS_PIPE_LD == 1
         if (c + 1 < 4) tmem_ld_wait(sr[c + 1]);
-#elif FO_WS_PIPE_LD == 2
-        if (c == 1) {
-          tmem_ld_wait(sr[2]);
-          tmem_ld_wait(sr[3]);
-        }
 #endif
       }
       const float mx = fmaxf(fmaxf(mxa, mxb), fmaxf(mxc, mxd));
@@ -241,61 +204,38 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       const float m_new = (m_cand - m_run > kRescaleThreshold) ? m_cand : m_run;
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
       const float alpha = (m_new == m_run) ? 1.f : fast_exp2(m_run - m_use);
-      // P = exp2(S * scale - m), written to tensor memory in kPPieces pieces.  Of every eight
-      // column pairs, kEmuPairs are exponentiated with a polynomial on the FMA pipe instead of
-      // ex2 on the special-function unit (16 lanes per clock per SM), which would otherwise
-      // bound this loop; tiles that carry a mask use ex2 throughout so masked entries are 0.
+      // P = exp2(S * scale - m): packed fp32 pairs for the multiply-add and the row sum, one
+      // unrolled block over the whole tile so that ex2 latencies overlap across chunks.
       const float2 sc2 = make_float2(prm.scale_log2, prm.scale_log2);
       const float2 nm2 = make_float2(-m_use, -m_use);
       float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
-      constexpr int kChunksPerPiece = 4 / kPPieces;  // 32-column chunks of S per piece
+      uint32_t pr[4][16];
 #pragma unroll
-      for (int piece = 0; piece < kPPieces; ++piece) {
-        uint32_t pr[16 * kChunksPerPiece];
+      for (int c = 0; c < 4; ++c) {
 #pragma unroll
-        for (int cc = 0; cc < kChunksPerPiece; ++cc) {
-          const int c = piece * kChunksPerPiece + cc;
-#pragma unroll
-          for (int q = 0; q < 16; ++q) {  // column pair q of the chunk
-            float2 x = __ffma2_rn(make_float2(__uint_as_float(sr[c][2 * q]), __uint_as_float(sr[c][2 * q + 1])), sc2, nm2);
-#if FO_WS_P_F16
-            // Round the exponent to fp16 and exponentiate both halves with one special-function
-            // instruction.  The row sum is taken in fp32 over these values; for fp16 inputs the
-            // packed result is P itself, for bf16 inputs it is re-rounded to bf16 (the MMA rejects
-            // an fp16 A operand next to a bf16 B operand: tried once, illegal instruction).
-            const uint32_t ph = exp2_f16x2(pack2<false>(x.x, x.y));
-            const float2 pf = __half22float2(*reinterpret_cast<const __half2*>(&ph));
-            if (q & 1) acc1 = __fadd2_rn(acc1, pf); else acc0 = __fadd2_rn(acc0, pf);
-            if constexpr (kBf16) pr[cc * 16 + q] = pack2<true>(pf.x, pf.y); else pr[cc * 16 + q] = ph;
-            continue;
-#endif
-            if ((q & 7) >= 8 - kEmuPairs && !need_mask) {
-              x = exp2_poly2(x);
-            } else {
-              x.x = fast_exp2(x.x);
-              x.y = fast_exp2(x.y);
-            }
-            if (q & 1) acc1 = __fadd2_rn(acc1, x); else acc0 = __fadd2_rn(acc0, x);
-            pr[cc * 16 + q] = pack2<kBf16>(x.x, x.y);
-          }
-          if (c == 0) {
-            // hand the rescale factor to the correction warps once the first exponentials are
-            // in flight (it is off this thread's critical path)
-            alpha_slot[(j & 1) * 128] = alpha;
-            mbar_arrive(bar_corr + s);
-            if ((warp & 3) == 0) trace_event(prm, s, j, 1);
-          }
+        for (int q = 0; q < 16; ++q) {  // column pair q of the chunk
+          float2 x = __ffma2_rn(make_float2(__uint_as_float(sr[c][2 * q]), __uint_as_float(sr[c][2 * q + 1])), sc2, nm2);
+          x.x = fast_exp2(x.x);
+          x.y = fast_exp2(x.y);
+          if (q & 1) acc1 = __fadd2_rn(acc1, x); else acc0 = __fadd2_rn(acc0, x);
+          pr[c][q] = pack2<kBf16>(x.x, x.y);
         }
-        if ((warp & 3) == 0 && piece == kPPieces - 1) trace_event(prm, s, j, 2);
-        // 16 packed columns per 32-column chunk of S
-#pragma unroll
-        for (int cc = 0; cc < kChunksPerPiece; ++cc)
-          tmem_st16(tS + (piece * kChunksPerPiece + cc) * 16, pr + cc * 16);
-        tcgen05_wait_st();
-        tcgen05_fence_before_sync();
-        mbar_arrive(bar_p_full + kMaxPPieces * s + piece);
-        if ((warp & 3) == 0 && piece == kPPieces - 1) trace_event(prm, s, j, 3);
+        if (c == 0) {
+          // hand the rescale factor to the correction warps once the first exponentials are in
+          // flight (it is off this thread's critical path)
+          alpha_slot[(j & 1) * 128] = alpha;
+          mbar_arrive(bar_corr + s);
+          if ((warp & 3) == 0) trace_event(prm, s, j, 1);
+        }
       }
+      if ((warp & 3) == 0) trace_event(prm, s, j, 2);
+      // P (two 16-bit values per column) over the first 64 columns of S
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_st16(tS + c * 16, pr[c]);
+      tcgen05_wait_st();
+      tcgen05_fence_before_sync();
+      mbar_arrive(bar_p_full + s);
+      if ((warp & 3) == 0) trace_event(prm, s, j, 3);
       const float rsum = (acc0.x + acc0.y) + (acc1.x + acc1.y);
       l_run = l_run * alpha + rsum;
       m_run = m_new;
@@ -400,27 +340,23 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           umma_ss_lo_elect(tS, a_lo + off, b_lo + off, idesc_qk, kk > 0 ? 1u : 0u);
         }
       };
-      // PV over one piece of the tile's keys: k-slices piece*8/kPPieces ...
-      auto issue_pv_piece = [&](int s, int stage, int piece, bool acc) {
+      // O_s (+)= P_s V over the V tile in ring slot `stage`
+      auto issue_pv = [&](int s, int stage, bool acc) {
         const uint32_t tP = tS0 + s * kBlockN;
         const uint32_t tO = tO0 + s * D;
         const uint32_t b_lo = kv_v_lo + stage * kStageStep;
 #pragma unroll
-        for (int k4 = 0; k4 < 8 / kPPieces; ++k4) {
-          const int kk = piece * (8 / kPPieces) + k4;
+        for (int kk = 0; kk < kBlockN / 16; ++kk) {
           // 16 key rows per slice: 2048 bytes of V, 8 packed columns of P
           umma_ts_lo_elect(tO, tP + kk * 8, b_lo + kk * 128, idesc_pv, (acc || kk > 0) ? 1u : 0u);
         }
       };
-      // waits for each piece of P_s of key tile j and issues its MMAs; the caller commits
+      // waits for P_s of key tile j (and for O_s to have been rescaled) and issues PV; the caller commits
       auto pv_tile = [&](int s, int stage, int j) {
         mbar_wait(bar_o_scaled + s, j & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_SOFTMAX);
-#pragma unroll
-        for (int piece = 0; piece < kPPieces; ++piece) {
-          mbar_wait(bar_p_full + kMaxPPieces * s + piece, j & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_SOFTMAX);
-          tcgen05_fence_after_sync();
-          issue_pv_piece(s, stage, piece, j > 0);
-        }
+        mbar_wait(bar_p_full + s, j & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_SOFTMAX);
+        tcgen05_fence_after_sync();
+        issue_pv(s, stage, j > 0);
       };
 
       mbar_wait(bar_q_full, 0, cta_abort, dstat, FO_STATUS_TIMEOUT_TMA);

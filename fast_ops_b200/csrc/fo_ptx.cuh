@@ -373,32 +373,4 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
-// exp2 of a packed pair of fp16 values in ONE special-function instruction (two results per
-// lane where the fp32 form gives one).
-__device__ __forceinline__ uint32_t exp2_f16x2(uint32_t x) {
-  uint32_t y;
-  asm("ex2.approx.f16x2 %0, %1;" : "=r"(y) : "r"(x));
-  return y;
-}
-
-// exp2 of two floats on the FMA pipe: x = n + f with n = round(x) (magic-number add), a cubic
-// for 2^f on [-0.5, 0.5] (maximum relative error 7.5e-5, fitted for this purpose), and n added
-// into the exponent field.  Inputs are clamped to >= -126; used where the result is about to
-// be rounded to a 16-bit type.
-__device__ __forceinline__ float2 exp2_poly2(float2 x) {
-  const float kMagic = 12582912.f;  // 1.5 * 2^23
-  x.x = fmaxf(x.x, -126.f);
-  x.y = fmaxf(x.y, -126.f);
-  const float2 r = __fadd2_rn(x, make_float2(kMagic, kMagic));
-  const float2 n = __fadd2_rn(r, make_float2(-kMagic, -kMagic));
-  const float2 f = __ffma2_rn(n, make_float2(-1.f, -1.f), x);
-  float2 p = __ffma2_rn(make_float2(0.05517132f, 0.05517132f), f, make_float2(0.24261054f, 0.24261054f));
-  p = __ffma2_rn(p, f, make_float2(0.69326097f, 0.69326097f));
-  p = __ffma2_rn(p, f, make_float2(0.99992812f, 0.99992812f));
-  float2 out;
-  out.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(r.x) << 23));
-  out.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(r.y) << 23));
-  return out;
-}
-
 }  // namespace fo
