@@ -59,8 +59,10 @@ template <int kRegs> __device__ __forceinline__ void reg_dealloc() {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs));
 }
 
-// grid = (num_q_pairs * B * H); block = 512.  Block w handles pair (num_pairs - 1 - w / (B*H)) of
-// head (w % (B*H)): with a causal mask the pairs with the most key tiles are scheduled first.
+// grid = (num_q_pairs * B * H); block = 512.  Block w handles pair (num_pairs - 1 - w % num_pairs)
+// of head (w / num_pairs): CTAs that run at the same time belong to two or three heads, whose K
+// and V stay in L2 while their query tiles sweep over them, and within a head the pairs with the
+// most key tiles (causal mask) start first.
 template <int D, bool kBf16>
 __global__ void __launch_bounds__(512, 1)
 attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -98,8 +100,14 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   const int lane = tid & 31;
   const int bh_count = prm.B * prm.H;
   const int num_pairs = (prm.num_q_tiles + 1) >> 1;
+#ifdef FO_WS_HEAD_MINOR
   const int pair = num_pairs - 1 - static_cast<int>(blockIdx.x) / bh_count;
   const int bh = static_cast<int>(blockIdx.x) % bh_count;
+#else
+  const int pair = num_pairs - 1 - static_cast<int>(blockIdx.x) % num_pairs;
+  const int bh = static_cast<int>(blockIdx.x) / num_pairs;
+  (void)bh_count;
+#endif
   const int b = bh / prm.H;
   const int h = bh - b * prm.H;
   const int n_kv_total = (prm.Sk + kBlockN - 1) / kBlockN;

@@ -34,10 +34,22 @@
 
 namespace {
 
-constexpr int kThreads = 256;
+#ifndef FO_LION_THREADS
+#define FO_LION_THREADS 256
+#endif
+#ifndef FO_LION_UNROLL
+#define FO_LION_UNROLL 4
+#endif
+#ifndef FO_LION_CTAS_PER_SM
+#define FO_LION_CTAS_PER_SM 0  // 0: ask the occupancy calculator
+#endif
+#ifndef FO_LION_STREAMING
+#define FO_LION_STREAMING 1  // 1: ld.global.cs / st.global.cs (evict-first), 0: default cache policy
+#endif
+constexpr int kThreads = FO_LION_THREADS;
 constexpr int kVec = 8;     // elements per thread per group (16 B of a 16-bit type)
-constexpr int kUnroll = 2;  // groups per thread per chunk
-constexpr int kChunk = kThreads * kVec * kUnroll;  // 4096 elements
+constexpr int kUnroll = FO_LION_UNROLL;  // groups per thread per chunk
+constexpr int kChunk = kThreads * kVec * kUnroll;  // 8192 elements
 
 struct LionTensor {
   void* p;
@@ -91,7 +103,11 @@ __device__ __forceinline__ void load_group(Group<T>& dst, const T* src) {
   const uint4* s = reinterpret_cast<const uint4*>(src);
   uint4* d = reinterpret_cast<uint4*>(dst.v);
 #pragma unroll
+#if FO_LION_STREAMING
   for (int i = 0; i < n16; ++i) d[i] = __ldcs(s + i);
+#else
+  for (int i = 0; i < n16; ++i) d[i] = s[i];
+#endif
 }
 
 template <typename T>
@@ -100,7 +116,11 @@ __device__ __forceinline__ void store_group(T* dst, const Group<T>& src) {
   uint4* d = reinterpret_cast<uint4*>(dst);
   const uint4* s = reinterpret_cast<const uint4*>(src.v);
 #pragma unroll
+#if FO_LION_STREAMING
   for (int i = 0; i < n16; ++i) __stcs(d + i, s[i]);
+#else
+  for (int i = 0; i < n16; ++i) d[i] = s[i];
+#endif
 }
 
 template <typename TP, typename TM>
@@ -251,8 +271,15 @@ template <typename TP, typename TM>
 int launch_typed(const Plan& plan, const LionConsts& c, cudaStream_t stream) {
   const LionTensor* tensors = static_cast<const LionTensor*>(plan.d_blob);
   const int64_t* chunk_start = reinterpret_cast<const int64_t*>(tensors + plan.n_tensors);
-  // Persistent grid: 8 CTAs of 256 threads fill an SM's 2048 thread slots.
-  int64_t grid = static_cast<int64_t>(sm_count(plan.device)) * 8;
+  // Persistent grid of exactly one resident wave: as many CTAs per SM as the kernel's register
+  // use allows, each striding over the chunks (a partial second wave costs up to 20 %).
+  int per_sm = FO_LION_CTAS_PER_SM;
+  if (per_sm == 0) {
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, lion_multi_tensor_kernel<TP, TM>, kThreads, 0) !=
+            cudaSuccess || per_sm < 1)
+      per_sm = 4;
+  }
+  int64_t grid = static_cast<int64_t>(sm_count(plan.device)) * per_sm;
   if (grid > plan.total_chunks) grid = plan.total_chunks;
   lion_multi_tensor_kernel<TP, TM><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
       tensors, chunk_start, plan.n_tensors, plan.total_chunks, c);
@@ -580,7 +607,13 @@ template <typename TP, typename TM>
 int launch_push(void* p, const void* g, void* m, int64_t begin, int64_t numel, const PeerList& peers,
                 const LionConsts& c, int device, cudaStream_t stream) {
   const int64_t total_chunks = (numel + kChunk - 1) / kChunk;
-  int64_t grid = static_cast<int64_t>(sm_count(device)) * 8;
+  int per_sm = FO_LION_CTAS_PER_SM;
+  if (per_sm == 0) {
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, lion_flat_push_kernel<TP, TM>, kThreads, 0) !=
+            cudaSuccess || per_sm < 1)
+      per_sm = 4;
+  }
+  int64_t grid = static_cast<int64_t>(sm_count(device)) * per_sm;
   if (grid > total_chunks) grid = total_chunks;
   lion_flat_push_kernel<TP, TM><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
       static_cast<TP*>(p), static_cast<const TP*>(g), static_cast<TM*>(m), begin, numel, peers, c);
