@@ -23,6 +23,7 @@ struct AttnParams {
   float scale_log2;  // softmax_scale * log2(e)
   int* device_status;
   int num_q_tiles;
+  int head_group;  // heads per scheduling group (>= 1)
   // Optional timeline of CTA 0 (debug): [role][key tile][event] SM clock values, or null.
   unsigned long long* trace;
 };

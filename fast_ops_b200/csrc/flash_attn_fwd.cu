@@ -241,6 +241,17 @@ extern "C" int fo_flash_attn_fwd(const void* q, const void* k, const void* v, vo
   prm.device_status = status;
   prm.num_q_tiles = (Sq + kBlockM - 1) / kBlockM;
   prm.trace = g_attn_trace;
+  {
+    // as many heads per group as keep their K and V (2 * Sk * D * 2 bytes each) within about a
+    // third of the 126 MB L2, leaving room for Q, O and the other traffic
+    const int64_t kv_bytes = 4LL * Sk * D;
+    int64_t g = (40LL << 20) / kv_bytes;
+    const char* e = std::getenv("FO_ATTN_HEAD_GROUP");
+    if (e) g = std::atoi(e);
+    if (g < 1) g = 1;
+    if (g > static_cast<int64_t>(B) * H) g = static_cast<int64_t>(B) * H;
+    prm.head_group = static_cast<int>(g);
+  }
 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool bf16 = dtype == FO_BF16;

@@ -59,10 +59,9 @@ template <int kRegs> __device__ __forceinline__ void reg_dealloc() {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs));
 }
 
-// grid = (num_q_pairs * B * H); block = 512.  Block w handles pair (num_pairs - 1 - w % num_pairs)
-// of head (w / num_pairs): CTAs that run at the same time belong to two or three heads, whose K
-// and V stay in L2 while their query tiles sweep over them, and within a head the pairs with the
-// most key tiles (causal mask) start first.
+// grid = (num_q_pairs * B * H); block = 512.  Consecutive blocks sweep a group of heads whose K
+// and V fit in L2 together, so the query tiles of those heads re-read K/V from L2 rather than
+// from HBM; within the group the pairs with the most key tiles (causal mask) start first.
 template <int D, bool kBf16>
 __global__ void __launch_bounds__(512, 1)
 attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -100,14 +99,14 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   const int lane = tid & 31;
   const int bh_count = prm.B * prm.H;
   const int num_pairs = (prm.num_q_tiles + 1) >> 1;
-#ifdef FO_WS_HEAD_MINOR
-  const int pair = num_pairs - 1 - static_cast<int>(blockIdx.x) / bh_count;
-  const int bh = static_cast<int>(blockIdx.x) % bh_count;
-#else
-  const int pair = num_pairs - 1 - static_cast<int>(blockIdx.x) % num_pairs;
-  const int bh = static_cast<int>(blockIdx.x) / num_pairs;
-  (void)bh_count;
-#endif
+  // Heads are taken in groups of prm.head_group (chosen on the host so that a group's K and V
+  // fit in L2); inside a group the blocks go pair-major, heaviest pairs of all its heads first.
+  const int group_blocks = prm.head_group * num_pairs;
+  const int group = static_cast<int>(blockIdx.x) / group_blocks;
+  const int in_group = static_cast<int>(blockIdx.x) - group * group_blocks;
+  const int heads_here = min(prm.head_group, bh_count - group * prm.head_group);
+  const int pair = num_pairs - 1 - in_group / heads_here;
+  const int bh = group * prm.head_group + in_group % heads_here;
   const int b = bh / prm.H;
   const int h = bh - b * prm.H;
   const int n_kv_total = (prm.Sk + kBlockN - 1) / kBlockN;
