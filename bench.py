@@ -40,6 +40,15 @@ ATTN = {
 }
 
 
+def measured_traffic(name):
+    """DRAM bytes per launch of the workload's kernel from the committed ncu summaries, or None."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "traffic.json")) as f:
+            return float(json.load(f)[name]["dram_bytes_per_launch"])
+    except Exception:
+        return None
+
+
 def load_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -223,7 +232,7 @@ def bench_attention(d: Dist, name: str, steps: int, warmup: int, peaks, with_e2e
     out = {
         "value": tflops_rank * d.world, "ms_per_step": ms, "gpu_launches": launches, "clocks": clocks,
         "roofline": {"bound": "tensor", "achieved": tflops_rank, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                     "frac": tflops_rank / peaks["bf16_tflops"], "traffic": None,
+                     "frac": tflops_rank / peaks["bf16_tflops"], "traffic": measured_traffic(name),
                      "peak_source": peaks["source"] + " cuBLAS bf16 burst",
                      "frac_of_sustained": tflops_rank / peaks["bf16_tflops_sustained"]},
         "config": {"workload": f"{name}: attention fwd B={B} H={H} S={S} D={D} bf16 causal={causal}, per GPU",
@@ -331,7 +340,8 @@ def bench_lion_c4(d: Dist, steps: int, warmup: int, peaks, with_e2e=True):
     res = {"workload": f"lion_c4: GPT-2-medium list, {len(shapes)} tensors, {n} params, fp32 p/g, bf16 m, per GPU",
            "value": gbs * d.world, "unit": "GB/s", "ms_per_step": ms, "gpu_launches": launches,
            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                        "frac": gbs / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"] + " copy"},
+                        "frac": gbs / peaks["hbm_gbs"], "traffic": measured_traffic("lion_c4"),
+                        "peak_source": peaks["source"] + " copy"},
            "e2e": {"value": n * 16 / (ms_e2e * 1e-3) / 1e9 * d.world, "unit": "GB/s",
                    "h2d_bytes_per_step": n * 4, "d2h_bytes_per_step": 4, "ms_per_step": ms_e2e}}
     del params, opt, hg
