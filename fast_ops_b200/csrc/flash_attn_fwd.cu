@@ -11,6 +11,7 @@
 #include "flash_attn_simple.cuh"
 #include "flash_attn_ws.cuh"
 #include "fo_host.h"
+#include "fo_tma.h"
 
 namespace {
 
@@ -19,51 +20,7 @@ using fo::kBlockM;
 using fo::kBlockN;
 using fo::kBoxCols;
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-// cuTensorMapEncodeTiled comes from the driver; resolving it through the runtime avoids
-// linking against libcuda.
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-  });
-  return fn;
-}
-
-// Tensor map over a (B, H, S, D) tensor with element strides (sb, sh, ss, 1): dimensions are
-// listed innermost first, the box is one [128 rows x 64 columns] swizzled tile, and reads
-// past S are filled with zeros.
-int make_tensor_map(CUtensorMap* map, const void* base, int dtype, int B, int H, int S, int D,
-                    const int64_t strides[3], const char* name) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return fo::fail(FO_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-  FO_REQUIRE((reinterpret_cast<uintptr_t>(base) & 15) == 0, "%s must be 16-byte aligned", name);
-  // A dimension of extent 1 never uses its stride; give it a harmless one.
-  int64_t sb = B > 1 ? strides[0] : static_cast<int64_t>(H) * S * D;
-  int64_t sh = H > 1 ? strides[1] : static_cast<int64_t>(S) * D;
-  int64_t ss = S > 1 ? strides[2] : D;
-  FO_REQUIRE(sb > 0 && sh > 0 && ss >= D, "%s: strides must be positive and rows must not overlap", name);
-  FO_REQUIRE(sb % 8 == 0 && sh % 8 == 0 && ss % 8 == 0, "%s: strides must be multiples of 8 elements", name);
-  const cuuint64_t dims[4] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(S), static_cast<cuuint64_t>(H),
-                              static_cast<cuuint64_t>(B)};
-  const cuuint64_t gstrides[3] = {static_cast<cuuint64_t>(ss) * 2, static_cast<cuuint64_t>(sh) * 2,
-                                  static_cast<cuuint64_t>(sb) * 2};
-  const cuuint32_t box[4] = {kBoxCols, kBlockN, 1, 1};
-  const cuuint32_t estr[4] = {1, 1, 1, 1};
-  const CUtensorMapDataType dt = dtype == FO_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  CUresult r = fn(map, dt, 4, const_cast<void*>(base), dims, gstrides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fo::fail(FO_ERR_CUDA, "cuTensorMapEncodeTiled(%s) failed with CUresult %d", name, (int)r);
-  return FO_OK;
-}
+using fo::make_tensor_map;
 
 // ---- one-tile self-test ------------------------------------------------------------------------
 // mode 0: C = A B^T, A (128 x K) and B (N x K) K-major through TMA (the QK^T path).

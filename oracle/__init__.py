@@ -5,6 +5,7 @@ leg of bench.py as the checker / timed CPU reference.  The product package
 (fast_ops_b200) never imports it.
 """
 from .oracle import (  # noqa: F401
+    attention_bwd,
     attention_fwd,
     build,
     lion_step,

@@ -261,3 +261,131 @@ void oracle_attention_fwd(const float* q, const float* k, const float* v, float*
   attn_ctx ctx = {q, k, v, out, lse, Sq, Sk, D, causal, bh_begin, row_begin, row_stride, rows_per_bh, scale};
   parallel_for((int64_t)(bh_end - bh_begin) * rows_per_bh, 16, attn_range, &ctx);
 }
+
+/* ---- attention backward ------------------------------------------------------------------
+ * Gradients of out = softmax(scale * q k^T [+ causal mask]) v with respect to q, k, v for a
+ * given d_out, all fp32 and dense (B,H,S,D): what torch autograd computes through
+ * fast_ops/flash_attention/attention_ref.py:41-67 (the way the reference's own tests obtain
+ * their expected gradients, tests/test_flash_attention_triton.py:118-131).
+ *   P = softmax(S),  dV = P^T dO,  dP = dO V^T,  dS = P o (dP - rowsum(dP o P)) * scale,
+ *   dQ = dS K,  dK = dS^T Q.
+ * Pass 1 runs over query rows (row statistics and dQ), pass 2 over keys (dK, dV), so no two
+ * threads ever add into the same output. */
+typedef struct {
+  const float *q, *k, *v, *dout;
+  float *dq, *dk, *dv, *lse, *delta;
+  int Sq, Sk, D, causal, bh_begin;
+  float scale;
+} attn_bwd_ctx;
+
+static void attn_bwd_rows(int64_t begin, int64_t end, void* vctx) {
+  const attn_bwd_ctx* c = (const attn_bwd_ctx*)vctx;
+  const int Sq = c->Sq, Sk = c->Sk, D = c->D;
+  float* p = (float*)malloc(sizeof(float) * (size_t)Sk);
+  float* o = (float*)malloc(sizeof(float) * (size_t)D);
+  float* acc = (float*)malloc(sizeof(float) * (size_t)D);
+  for (int64_t r = begin; r < end; ++r) {
+    const int bh = c->bh_begin + (int)(r / Sq);
+    const int i = (int)(r % Sq);
+    const float* qi = c->q + ((int64_t)bh * Sq + i) * D;
+    const float* doi = c->dout + ((int64_t)bh * Sq + i) * D;
+    const float* kb = c->k + (int64_t)bh * Sk * D;
+    const float* vb = c->v + (int64_t)bh * Sk * D;
+    int n = Sk;
+    if (c->causal && i + 1 < n) n = i + 1;
+    float mx = -INFINITY;
+    for (int j = 0; j < n; ++j) {
+      const float* kj = kb + (int64_t)j * D;
+      float s = 0.f;
+#pragma omp simd reduction(+ : s)
+      for (int d = 0; d < D; ++d) s += qi[d] * kj[d];
+      s *= c->scale;
+      p[j] = s;
+      if (s > mx) mx = s;
+    }
+    float sum = 0.f;
+    for (int j = 0; j < n; ++j) {
+      p[j] = expf(p[j] - mx);
+      sum += p[j];
+    }
+    const float inv = 1.f / sum;
+    for (int d = 0; d < D; ++d) o[d] = 0.f;
+    for (int j = 0; j < n; ++j) {
+      p[j] *= inv;
+      const float* vj = vb + (int64_t)j * D;
+#pragma omp simd
+      for (int d = 0; d < D; ++d) o[d] += p[j] * vj[d];
+    }
+    float delta = 0.f;
+    for (int d = 0; d < D; ++d) delta += o[d] * doi[d];
+    c->lse[(int64_t)bh * Sq + i] = mx + logf(sum);
+    c->delta[(int64_t)bh * Sq + i] = delta;
+    for (int d = 0; d < D; ++d) acc[d] = 0.f;
+    for (int j = 0; j < n; ++j) {
+      const float* vj = vb + (int64_t)j * D;
+      const float* kj = kb + (int64_t)j * D;
+      float dp = 0.f;
+#pragma omp simd reduction(+ : dp)
+      for (int d = 0; d < D; ++d) dp += doi[d] * vj[d];
+      const float ds = p[j] * (dp - delta) * c->scale;
+#pragma omp simd
+      for (int d = 0; d < D; ++d) acc[d] += ds * kj[d];
+    }
+    float* dqi = c->dq + ((int64_t)bh * Sq + i) * D;
+    for (int d = 0; d < D; ++d) dqi[d] = acc[d];
+  }
+  free(p);
+  free(o);
+  free(acc);
+}
+
+static void attn_bwd_keys(int64_t begin, int64_t end, void* vctx) {
+  const attn_bwd_ctx* c = (const attn_bwd_ctx*)vctx;
+  const int Sq = c->Sq, Sk = c->Sk, D = c->D;
+  float* ak = (float*)malloc(sizeof(float) * (size_t)D);
+  float* av = (float*)malloc(sizeof(float) * (size_t)D);
+  for (int64_t r = begin; r < end; ++r) {
+    const int bh = c->bh_begin + (int)(r / Sk);
+    const int j = (int)(r % Sk);
+    const float* kj = c->k + ((int64_t)bh * Sk + j) * D;
+    const float* vj = c->v + ((int64_t)bh * Sk + j) * D;
+    for (int d = 0; d < D; ++d) ak[d] = av[d] = 0.f;
+    for (int i = c->causal ? j : 0; i < Sq; ++i) {
+      const float* qi = c->q + ((int64_t)bh * Sq + i) * D;
+      const float* doi = c->dout + ((int64_t)bh * Sq + i) * D;
+      float s = 0.f, dp = 0.f;
+#pragma omp simd reduction(+ : s, dp)
+      for (int d = 0; d < D; ++d) {
+        s += qi[d] * kj[d];
+        dp += doi[d] * vj[d];
+      }
+      const float p = expf(s * c->scale - c->lse[(int64_t)bh * Sq + i]);
+      const float ds = p * (dp - c->delta[(int64_t)bh * Sq + i]) * c->scale;
+#pragma omp simd
+      for (int d = 0; d < D; ++d) {
+        av[d] += p * doi[d];
+        ak[d] += ds * qi[d];
+      }
+    }
+    float* dkj = c->dk + ((int64_t)bh * Sk + j) * D;
+    float* dvj = c->dv + ((int64_t)bh * Sk + j) * D;
+    for (int d = 0; d < D; ++d) {
+      dkj[d] = ak[d];
+      dvj[d] = av[d];
+    }
+  }
+  free(ak);
+  free(av);
+}
+
+/* lse and delta are scratch of B*H*Sq floats supplied by the caller. */
+void oracle_attention_bwd(const float* q, const float* k, const float* v, const float* dout, float* dq,
+                          float* dk, float* dv, float* lse, float* delta, int B, int H, int Sq, int Sk,
+                          int D, int causal, float scale, int bh_begin, int bh_end) {
+  if (bh_begin < 0) bh_begin = 0;
+  if (bh_end > B * H) bh_end = B * H;
+  if (bh_end <= bh_begin || Sq <= 0 || Sk <= 0) return;
+  attn_bwd_ctx ctx = {q, k, v, dout, dq, dk, dv, lse, delta, Sq, Sk, D, causal, bh_begin, scale};
+  parallel_for((int64_t)(bh_end - bh_begin) * Sq, 8, attn_bwd_rows, &ctx);
+  parallel_for((int64_t)(bh_end - bh_begin) * Sk, 8, attn_bwd_keys, &ctx);
+}

@@ -41,6 +41,9 @@ def _load() -> ctypes.CDLL:
             ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
             ctypes.c_float, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int]
         lib.oracle_attention_fwd.restype = None
+        lib.oracle_attention_bwd.argtypes = [ctypes.c_void_p] * 9 + [ctypes.c_int] * 6 + [
+            ctypes.c_float, ctypes.c_int, ctypes.c_int]
+        lib.oracle_attention_bwd.restype = None
         lib.oracle_num_threads.restype = ctypes.c_int
         lib.oracle_set_num_threads.argtypes = [ctypes.c_int]
         _lib = lib
@@ -95,3 +98,24 @@ def attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: boo
                                  B, H, Sq, Sk, D, int(bool(causal)), float(softmax_scale), int(b), int(e),
                                  int(r0), int(r1), int(rs))
     return out, lse
+
+
+def attention_bwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, dout: torch.Tensor, causal: bool = False,
+                  softmax_scale: Optional[float] = None,
+                  bh_range: Optional[Tuple[int, int]] = None) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """(dq, dk, dv) of softmax(scale * q k^T [+ causal mask]) v for the output gradient `dout`,
+    in fp32 on the CPU: what autograd yields through fast_ops/flash_attention/attention_ref.py.
+    Shapes as attention_fwd; with `bh_range` only those (batch*head) slices are filled."""
+    B, H, Sq, D = q.shape
+    Sk = k.shape[2]
+    if softmax_scale is None:
+        softmax_scale = 1.0 / (D ** 0.5)
+    qf, kf, vf, df = (t.detach().to("cpu", torch.float32).contiguous() for t in (q, k, v, dout))
+    dq, dk, dv = torch.zeros_like(qf), torch.zeros_like(kf), torch.zeros_like(vf)
+    lse = torch.zeros(B, H, Sq)
+    delta = torch.zeros(B, H, Sq)
+    b, e = bh_range if bh_range is not None else (0, B * H)
+    _load().oracle_attention_bwd(qf.data_ptr(), kf.data_ptr(), vf.data_ptr(), df.data_ptr(), dq.data_ptr(),
+                                 dk.data_ptr(), dv.data_ptr(), lse.data_ptr(), delta.data_ptr(), B, H, Sq, Sk, D,
+                                 int(bool(causal)), float(softmax_scale), int(b), int(e))
+    return dq, dk, dv

@@ -2,7 +2,7 @@
 
 Run once, in a container where the reference checkout is importable:
 
-    python tests/golden/make_golden.py /path/to/fast-ops
+    python tests/golden/make_golden.py /path/to/fast-ops [attention|attention_bwd|lion]
 
 It imports fast_ops.flash_attention.attention_ref.attention_ref and
 fast_ops.lion.lion_optimizer_ref.Lion from that checkout, feeds them seeded inputs and stores
@@ -83,6 +83,32 @@ def make_attention(attention_ref):
         print("attention", name, out.shape, "stored rows", len(rows))
 
 
+def make_attention_bwd(attention_ref):
+    """Gradients through the reference's attention_ref by autograd, the way the reference's own
+    tests obtain them (tests/test_flash_attention_triton.py:118-131)."""
+    cases = [
+        # name, seed, B, H, Sq, Sk, D, input dtype, causal
+        ("s256d64_bf16_causal", 11, 1, 2, 256, 256, 64, "bf16", True),
+        ("s200d128_f16_causal_ragged", 12, 1, 1, 200, 200, 128, "f16", True),
+        ("sq130sk300d64_bf16_full", 13, 1, 2, 130, 300, 64, "bf16", False),
+        ("s384d128_bf16_full", 14, 1, 1, 384, 384, 128, "bf16", False),
+    ]
+    for name, seed, B, H, Sq, Sk, D, dt, causal in cases:
+        q, k, v = attention_inputs(seed, B, H, Sq, Sk, D, DT[dt])
+        gen = torch.Generator().manual_seed(seed + 1000)
+        dout = torch.randn(B, H, Sq, D, generator=gen).to(DT[dt])
+        qf, kf, vf = (t.float().transpose(1, 2).requires_grad_(True) for t in (q, k, v))
+        out, _ = attention_ref(qf, kf, vf, causal=causal, upcast=True)
+        out.backward(dout.float().transpose(1, 2))
+        np.savez_compressed(
+            os.path.join(HERE, f"attnbwd_{name}.npz"),
+            seed=seed, shape=np.array([B, H, Sq, Sk, D]), dtype=dt, causal=causal,
+            input_sha256=digest(q, k, v, dout),
+            dq=qf.grad.transpose(1, 2).contiguous().numpy(), dk=kf.grad.transpose(1, 2).contiguous().numpy(),
+            dv=vf.grad.transpose(1, 2).contiguous().numpy())
+        print("attention backward", name)
+
+
 def make_lion(LionRef):
     n = 2048
     cases = [
@@ -135,8 +161,13 @@ def main():
     from fast_ops.lion.lion_optimizer_ref import Lion as LionRef
 
     torch.set_num_threads(1)
-    make_attention(attention_ref)
-    make_lion(LionRef)
+    only = sys.argv[2] if len(sys.argv) > 2 else "all"
+    if only in ("all", "attention"):
+        make_attention(attention_ref)
+    if only in ("all", "attention_bwd"):
+        make_attention_bwd(attention_ref)
+    if only in ("all", "lion"):
+        make_lion(LionRef)
 
 
 if __name__ == "__main__":

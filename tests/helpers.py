@@ -61,3 +61,9 @@ def ulp_distance(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
 def bf16_ulp_distance(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     """Distance in bf16 ulps (the unit the parity bar is stated in), for any float dtype."""
     return (ordered_int(a.float().bfloat16()) - ordered_int(b.float().bfloat16())).abs()
+
+
+def attention_dout(seed, B, H, Sq, D, dtype):
+    """The generator's recipe for the output gradient of the backward vectors."""
+    gen = torch.Generator().manual_seed(int(seed) + 1000)
+    return torch.randn(B, H, Sq, D, generator=gen).to(dtype)

@@ -78,3 +78,19 @@ def test_attention_oracle_row_sampling():
     mask = torch.ones(50, dtype=torch.bool)
     mask[rows] = False
     assert part[:, :, mask].abs().sum() == 0
+
+
+@pytest.mark.parametrize("path", golden_files("attnbwd"), ids=lambda p: p.split("attnbwd_")[-1][:-4])
+def test_attention_backward_oracle_matches_reference_autograd(path):
+    from helpers import attention_dout
+
+    z = np.load(path)
+    B, H, Sq, Sk, D = (int(x) for x in z["shape"])
+    dt = DT[str(z["dtype"])]
+    q, k, v = attention_inputs(int(z["seed"]), B, H, Sq, Sk, D, dt)
+    dout = attention_dout(int(z["seed"]), B, H, Sq, D, dt)
+    assert input_digest(q, k, v, dout) == str(z["input_sha256"])
+    dq, dk, dv = oracle.attention_bwd(q, k, v, dout, causal=bool(z["causal"]))
+    for name, got in (("dq", dq), ("dk", dk), ("dv", dv)):
+        want = torch.from_numpy(z[name])
+        assert torch.allclose(got, want, atol=1e-5, rtol=1e-4), f"{name}: {(got - want).abs().max()}"
