@@ -1,0 +1,319 @@
+// Attention backward for sm_100a: dQ, dK, dV from dO, Q, K, V and the forward's LSE.
+//
+// The reference's CUDA path has no backward (fast_ops/flash_attention/flash_attention.py:41-45
+// raises); the semantics follow its complete implementation
+// (fast_ops/flash_attention/flash_attention_triton.py:273-315 for delta = rowsum(O o dO),
+// :322-638 for the main loop): one CTA owns a 128-key tile, keeps dK and dV for it in tensor
+// memory, walks the query tiles that see those keys, and adds its share of dQ into an fp32
+// buffer with atomics (as the reference does, :610).
+//
+// Per query tile, five tcgen05 MMAs (all fp32 accumulation in tensor memory):
+//   S  = Q K^T          (Q, K K-major from shared memory)
+//   dP = dO V^T         (dO, V K-major)
+//   -- threads: P = exp2(S*scale - LSE), dS = P o (dP - delta) * scale, both written to shared
+//      memory as 16-bit [query row][key] tiles in the 128-byte-swizzled layout --
+//   dV += P^T dO        (P as the M-major A operand, dO as the N-major B operand)
+//   dK += dS^T Q        (dS M-major A, Q N-major B)
+//   dQ  = dS K          (dS K-major A, K N-major B), read back and added to the fp32 dQ buffer
+//
+// Warps 0-3: one thread per query row (and per key row in the epilogue); warp 4 issues the MMAs;
+// warp 5 issues the TMA loads.  This first version runs the steps of a query tile in order, with
+// no overlap between tiles.
+#pragma once
+
+#include "flash_attn_common.cuh"
+#include "fo_host.h"
+
+namespace fo {
+
+struct AttnBwdParams {
+  const float* lse;    // (B, H, Sq) natural-log LSE of the forward
+  const float* delta;  // (B, H, Sq) rowsum(O o dO)
+  float* dq_accum;     // (B, H, Sq, D) fp32, zeroed before the launch
+  void* dk;
+  void* dv;
+  int64_t dk_stride_b, dk_stride_h, dk_stride_s;
+  int64_t dv_stride_b, dv_stride_h, dv_stride_s;
+  int B, H, Sq, Sk;
+  int causal;
+  float scale;       // softmax scale
+  float scale_log2;  // scale * log2(e)
+  int* device_status;
+};
+
+template <int D>
+struct BwdConfig {
+  static constexpr int kTileBytes = kBlockM * D * 2;  // Q, dO, K, V tiles
+  static constexpr int kPBytes = kBlockM * kBlockN * 2;  // P and dS: [128 rows][128 keys] 16-bit
+  static constexpr int kOffK = 0;
+  static constexpr int kOffV = kTileBytes;
+  static constexpr int kOffQ = 2 * kTileBytes;
+  static constexpr int kOffDO = 3 * kTileBytes;
+  static constexpr int kOffP = 4 * kTileBytes;
+  static constexpr int kOffDS = kOffP + kPBytes;
+  static constexpr int kOffBars = kOffDS + kPBytes;
+  static constexpr int kNumBars = 7;
+  static constexpr int kOffMisc = kOffBars + kNumBars * 8;
+  static constexpr int kSmemBytes = kOffMisc + 64 + 1024;
+  static constexpr uint32_t kTmemCols = 512;
+  static constexpr uint32_t kColDK = 0, kColDV = D, kColS = 256, kColDP = 384;  // dQ reuses kColS
+};
+
+// Writes 8 consecutive 16-bit values (one 16-byte unit) of row `r`, unit `u` (0..15 over 128
+// columns) of a [128 x 128] tile stored as two [128 x 64] boxes with the 128-byte swizzle.
+__device__ __forceinline__ void store_swizzled_unit(uint8_t* tile, int r, int u, uint4 v) {
+  const int box = u >> 3;
+  const int slot = (u & 7) ^ (r & 7);
+  *reinterpret_cast<uint4*>(tile + box * kBoxBytes + r * 128 + slot * 16) = v;
+}
+
+// grid = (key tiles, B*H); block = 192.
+template <int D, bool kBf16>
+__global__ void __launch_bounds__(192, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
+                const AttnBwdParams prm) {
+  using Cfg = BwdConfig<D>;
+  constexpr int kTileBytes = Cfg::kTileBytes;
+  constexpr int kBoxes = D / kBoxCols;
+
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint8_t* sK = smem + Cfg::kOffK;
+  uint8_t* sV = smem + Cfg::kOffV;
+  uint8_t* sQ = smem + Cfg::kOffQ;
+  uint8_t* sDO = smem + Cfg::kOffDO;
+  uint8_t* sP = smem + Cfg::kOffP;
+  uint8_t* sDS = smem + Cfg::kOffDS;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kOffBars);
+  uint64_t* bar_kv = bars + 0;        // TMA -> MMA: K and V of this CTA are in shared memory
+  uint64_t* bar_q_full = bars + 1;    // TMA -> MMA: Q_i and dO_i loaded
+  uint64_t* bar_q_empty = bars + 2;   // MMA -> TMA: every MMA reading Q_i / dO_i has completed
+  uint64_t* bar_s_full = bars + 3;    // MMA -> threads: S and dP are in tensor memory
+  uint64_t* bar_pds_full = bars + 4;  // threads -> MMA: P and dS are in shared memory (128 arrivals)
+  uint64_t* bar_dq_full = bars + 5;   // MMA -> threads: dQ tile (and dK, dV so far) complete
+  uint64_t* bar_s_free = bars + 6;    // threads -> MMA: dQ read, S / dP columns reusable (128 arrivals)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::kOffMisc);
+  volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* skip = cta_abort + 1;
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int j = blockIdx.x;  // key tile
+  const int bh = blockIdx.y;
+  const int b = bh / prm.H;
+  const int h = bh - b * prm.H;
+  const int k0 = j * kBlockN;
+  const int n_q_tiles = (prm.Sq + kBlockM - 1) / kBlockM;
+  // query tiles that see this key tile: all of them, or with a causal mask those whose last
+  // row is not above the tile's first key
+  const int i0 = prm.causal ? min(j, n_q_tiles) : 0;
+  const int n_iter = n_q_tiles - i0;
+  int* const dstat = prm.device_status;
+
+  if (tid == 0) {
+    *cta_abort = 0;
+    *skip = *reinterpret_cast<volatile int*>(prm.device_status);
+    mbar_init(bar_kv, 1);
+    mbar_init(bar_q_full, 1);
+    mbar_init(bar_q_empty, 1);
+    mbar_init(bar_s_full, 1);
+    mbar_init(bar_pds_full, 128);
+    mbar_init(bar_dq_full, 1);
+    mbar_init(bar_s_free, 128);
+    fence_mbar_init();
+    prefetch_tensormap(&tm_q);
+    prefetch_tensormap(&tm_k);
+    prefetch_tensormap(&tm_v);
+    prefetch_tensormap(&tm_do);
+  }
+  __syncthreads();
+  if (*skip) return;
+  if (warp == 4) {
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish_alloc_permit();
+  }
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  tcgen05_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp < 4) {
+    // ================================ compute threads ================================
+    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t tS = tmem_base + Cfg::kColS + lane_base;
+    const uint32_t tDP = tmem_base + Cfg::kColDP + lane_base;
+    for (int it = 0; it < n_iter; ++it) {
+      const int i = i0 + it;
+      const int q0 = i * kBlockM;
+      const int row = q0 + tid;
+      const bool row_ok = row < prm.Sq;
+      // a row past the end gets LSE = +inf, so its P and dS are exactly 0
+      const float lse2 = row_ok ? prm.lse[static_cast<int64_t>(bh) * prm.Sq + row] * 1.4426950408889634f : INFINITY;
+      const float delta = row_ok ? prm.delta[static_cast<int64_t>(bh) * prm.Sq + row] : 0.f;
+      const bool need_mask = (k0 + kBlockN > prm.Sk) || (prm.causal && k0 + kBlockN - 1 > q0);
+      mbar_wait(bar_s_full, it & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_MMA);
+      tcgen05_fence_after_sync();
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t sr[32], dpr[32];
+        tmem_ld32(tS + c * 32, sr);
+        tmem_ld32(tDP + c * 32, dpr);
+        tmem_ld_wait(sr);
+        tmem_ld_wait(dpr);
+        uint32_t pp[16], dd[16];
+#pragma unroll
+        for (int x = 0; x < 32; x += 2) {
+          float p0 = fast_exp2(fmaf(__uint_as_float(sr[x]), prm.scale_log2, -lse2));
+          float p1 = fast_exp2(fmaf(__uint_as_float(sr[x + 1]), prm.scale_log2, -lse2));
+          if (need_mask) {
+            const int col = k0 + c * 32 + x;
+            if (col >= prm.Sk || (prm.causal && col > row)) p0 = 0.f;
+            if (col + 1 >= prm.Sk || (prm.causal && col + 1 > row)) p1 = 0.f;
+          }
+          const float d0 = p0 * (__uint_as_float(dpr[x]) - delta) * prm.scale;
+          const float d1 = p1 * (__uint_as_float(dpr[x + 1]) - delta) * prm.scale;
+          pp[x >> 1] = pack2<kBf16>(p0, p1);
+          dd[x >> 1] = pack2<kBf16>(d0, d1);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          store_swizzled_unit(sP, tid, c * 4 + u, make_uint4(pp[4 * u], pp[4 * u + 1], pp[4 * u + 2], pp[4 * u + 3]));
+          store_swizzled_unit(sDS, tid, c * 4 + u, make_uint4(dd[4 * u], dd[4 * u + 1], dd[4 * u + 2], dd[4 * u + 3]));
+        }
+      }
+      // shared-memory writes of these threads must be visible to the tensor core's reads
+      fence_proxy_async_smem();
+      tcgen05_fence_before_sync();
+      mbar_arrive(bar_pds_full);
+
+      // dQ tile of this (query tile, key tile) pair -> fp32 accumulation buffer
+      mbar_wait(bar_dq_full, it & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_MMA);
+      tcgen05_fence_after_sync();
+      float* dq_row = prm.dq_accum + (static_cast<int64_t>(bh) * prm.Sq + row) * D;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t qr[32];
+        tmem_ld32(tS + c * 32, qr);
+        tmem_ld_wait(qr);
+        if (row_ok) {
+#pragma unroll
+          for (int x = 0; x < 32; ++x) atomicAdd(dq_row + c * 32 + x, __uint_as_float(qr[x]));
+        }
+      }
+      tcgen05_fence_before_sync();
+      mbar_arrive(bar_s_free);
+    }
+
+    // ---- epilogue: dK, dV of key row (k0 + tid) ----
+    const int kv_row = k0 + tid;
+    const bool kv_ok = kv_row < prm.Sk;
+    uint16_t* dk_row = static_cast<uint16_t*>(prm.dk) + b * prm.dk_stride_b + h * prm.dk_stride_h +
+                       static_cast<int64_t>(kv_row) * prm.dk_stride_s;
+    uint16_t* dv_row = static_cast<uint16_t*>(prm.dv) + b * prm.dv_stride_b + h * prm.dv_stride_h +
+                       static_cast<int64_t>(kv_row) * prm.dv_stride_s;
+    if (n_iter > 0) tcgen05_fence_after_sync();
+#pragma unroll
+    for (int which = 0; which < 2; ++which) {
+      const uint32_t tAcc = tmem_base + (which ? Cfg::kColDV : Cfg::kColDK) + lane_base;
+      uint16_t* out_row = which ? dv_row : dk_row;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t ar[32];
+        if (n_iter > 0) {
+          tmem_ld32(tAcc + c * 32, ar);
+          tmem_ld_wait(ar);
+        } else {
+#pragma unroll
+          for (int x = 0; x < 32; ++x) ar[x] = 0;  // no query tile sees these keys
+        }
+        if (kv_ok) {
+#pragma unroll
+          for (int x = 0; x < 32; x += 8) {
+            uint4 v;
+            v.x = pack2<kBf16>(__uint_as_float(ar[x + 0]), __uint_as_float(ar[x + 1]));
+            v.y = pack2<kBf16>(__uint_as_float(ar[x + 2]), __uint_as_float(ar[x + 3]));
+            v.z = pack2<kBf16>(__uint_as_float(ar[x + 4]), __uint_as_float(ar[x + 5]));
+            v.w = pack2<kBf16>(__uint_as_float(ar[x + 6]), __uint_as_float(ar[x + 7]));
+            *reinterpret_cast<uint4*>(out_row + c * 32 + x) = v;
+          }
+        }
+      }
+    }
+  } else if (warp == 4) {
+    // ================================ MMA issuer ================================
+    constexpr uint32_t idesc_s = make_idesc(kBf16, kBlockM, kBlockN, 0, 0);  // S, dP: both K-major
+    constexpr uint32_t idesc_t = make_idesc(kBf16, kBlockM, D, 1, 1);        // dV, dK: A M-major, B N-major
+    constexpr uint32_t idesc_q = make_idesc(kBf16, kBlockM, D, 0, 1);        // dQ: A K-major, B N-major
+    constexpr uint32_t kBoxStep = kBoxBytes >> 4;
+    const uint32_t q_k = desc_lo(smem_u32(sQ), 16), do_k = desc_lo(smem_u32(sDO), 16);
+    const uint32_t k_k = desc_lo(smem_u32(sK), 16), v_k = desc_lo(smem_u32(sV), 16);
+    const uint32_t q_n = desc_lo(smem_u32(sQ), kBoxBytes), do_n = desc_lo(smem_u32(sDO), kBoxBytes);
+    const uint32_t k_n = desc_lo(smem_u32(sK), kBoxBytes);
+    const uint32_t p_m = desc_lo(smem_u32(sP), kBoxBytes), ds_m = desc_lo(smem_u32(sDS), kBoxBytes);
+    const uint32_t ds_k = desc_lo(smem_u32(sDS), 16);
+    const uint32_t tDK = tmem_base + Cfg::kColDK, tDV = tmem_base + Cfg::kColDV;
+    const uint32_t tS = tmem_base + Cfg::kColS, tDP = tmem_base + Cfg::kColDP;
+
+    mbar_wait(bar_kv, 0, cta_abort, dstat, FO_STATUS_TIMEOUT_TMA);
+    for (int it = 0; it < n_iter; ++it) {
+      mbar_wait(bar_q_full, it & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_TMA);
+      if (it > 0) mbar_wait(bar_s_free, (it - 1) & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_SOFTMAX);
+      tcgen05_fence_after_sync();
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {  // S = Q K^T, dP = dO V^T  (K = head_dim)
+        const uint32_t off = (kk >> 2) * kBoxStep + (kk & 3) * 2;
+        umma_ss_lo_elect(tS, q_k + off, k_k + off, idesc_s, kk > 0 ? 1u : 0u);
+      }
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        const uint32_t off = (kk >> 2) * kBoxStep + (kk & 3) * 2;
+        umma_ss_lo_elect(tDP, do_k + off, v_k + off, idesc_s, kk > 0 ? 1u : 0u);
+      }
+      tcgen05_commit_elect(bar_s_full);
+
+      mbar_wait(bar_pds_full, it & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_SOFTMAX);
+      tcgen05_fence_after_sync();
+#pragma unroll
+      for (int kk = 0; kk < kBlockM / 16; ++kk)  // dV += P^T dO  (K = 16 query rows per step: 2048 bytes)
+        umma_ss_lo_elect(tDV, p_m + kk * 128, do_n + kk * 128, idesc_t, (it > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+      for (int kk = 0; kk < kBlockM / 16; ++kk)  // dK += dS^T Q
+        umma_ss_lo_elect(tDK, ds_m + kk * 128, q_n + kk * 128, idesc_t, (it > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+      for (int kk = 0; kk < kBlockN / 16; ++kk) {  // dQ = dS K  (K = 16 keys per step), over the S columns
+        const uint32_t off = (kk >> 2) * kBoxStep + (kk & 3) * 2;
+        umma_ss_lo_elect(tS, ds_k + off, k_n + kk * 128, idesc_q, kk > 0 ? 1u : 0u);
+      }
+      tcgen05_commit_elect(bar_q_empty);
+      tcgen05_commit_elect(bar_dq_full);
+    }
+  } else {
+    // ================================ TMA producer ================================
+    const bool issuer = lane == 0;
+    if (issuer) {
+      mbar_arrive_expect_tx(bar_kv, 2 * kTileBytes);
+      for (int c = 0; c < kBoxes; ++c) tma_load_4d(sK + c * kBoxBytes, &tm_k, bar_kv, c * kBoxCols, k0, h, b);
+      for (int c = 0; c < kBoxes; ++c) tma_load_4d(sV + c * kBoxBytes, &tm_v, bar_kv, c * kBoxCols, k0, h, b);
+    }
+    __syncwarp();
+    for (int it = 0; it < n_iter; ++it) {
+      if (it > 0) mbar_wait(bar_q_empty, (it - 1) & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_MMA);
+      if (issuer) {
+        const int q0 = (i0 + it) * kBlockM;
+        mbar_arrive_expect_tx(bar_q_full, 2 * kTileBytes);
+        for (int c = 0; c < kBoxes; ++c) tma_load_4d(sQ + c * kBoxBytes, &tm_q, bar_q_full, c * kBoxCols, q0, h, b);
+        for (int c = 0; c < kBoxes; ++c) tma_load_4d(sDO + c * kBoxBytes, &tm_do, bar_q_full, c * kBoxCols, q0, h, b);
+      }
+      __syncwarp();
+    }
+    if (n_iter == 0) mbar_wait(bar_kv, 0, cta_abort, dstat, FO_STATUS_TIMEOUT_TMA);  // drain the K/V load before exit
+  }
+
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  if (warp == 4) tmem_dealloc(tmem_base, Cfg::kTmemCols);
+}
+
+}  // namespace fo

@@ -3,7 +3,8 @@
 Mirrors fast_ops/flash_attention/flash_attention.py of jfc4050/fast-ops:
 `multi_head_attention(Q, K, V)` (:48-77) and `FlashAttentionFunction` (:28-45) keep their
 names, argument meaning, (B, H, S, D) layout and error behaviour (a constraint violation
-raises).  The keyword-only extras (`causal`, `softmax_scale`, `return_lse`) follow the
+raises), except that `backward`, a placeholder that raises in the reference, is implemented.
+The keyword-only extras (`causal`, `softmax_scale`, `return_lse`) follow the
 reference's complete forward (flash_attention_triton.py:720-731); the default call is the
 reference call.
 """
@@ -76,16 +77,83 @@ def flash_attention_forward(Q: Tensor, K: Tensor, V: Tensor, *, causal: bool = F
     return (O, lse) if return_lse else O
 
 
+def flash_attention_backward(dO: Tensor, Q: Tensor, K: Tensor, V: Tensor, O: Tensor, LSE: Tensor, *,
+                             causal: bool = False,
+                             softmax_scale: Optional[float] = None) -> Tuple[Tensor, Tensor, Tensor]:
+    """(dQ, dK, dV) for the output gradient dO, from the forward's inputs, output O and LSE.
+
+    Shapes and dtypes as in `flash_attention_forward`; LSE is the (B, H, M) fp32 tensor that call
+    returns with `return_lse=True`.  Semantics of the reference's complete backward
+    (fast_ops/flash_attention/flash_attention_triton.py:832-958).
+    """
+    for name, t in (("dO", dO), ("Q", Q), ("K", K), ("V", V), ("O", O)):
+        if not t.is_cuda or t.dim() != 4 or t.dtype != Q.dtype or t.device != Q.device:
+            raise RuntimeError(f"{name} must be a 4-D CUDA tensor with Q's dtype and device")
+        if t.stride(3) != 1:
+            raise RuntimeError(f"{name}: the last dimension must be contiguous")
+    if Q.dtype not in (torch.float16, torch.bfloat16):
+        raise RuntimeError(f"inputs must be float16 or bfloat16, got {Q.dtype}")
+    B, H, M, D = Q.shape
+    N = K.shape[2]
+    if dO.shape != Q.shape or O.shape != Q.shape or V.shape != K.shape or K.shape[:2] != (B, H) or K.shape[3] != D:
+        raise RuntimeError("shape mismatch between dO, Q, K, V, O")
+    if LSE.shape != (B, H, M) or LSE.dtype != torch.float32 or not LSE.is_contiguous() or LSE.device != Q.device:
+        raise RuntimeError("LSE must be a contiguous (B, H, M) float32 tensor on Q's device")
+    scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(D)
+    dQ, dK, dV = torch.empty_like(Q), torch.empty_like(K), torch.empty_like(V)
+    for t in (dQ, dK, dV):
+        if t.stride(3) != 1:
+            raise RuntimeError("gradient layout: the last dimension must be contiguous")
+    dq_accum = torch.empty((B, H, M, D), dtype=torch.float32, device=Q.device)
+    delta = torch.empty((B, H, M), dtype=torch.float32, device=Q.device)
+    lib = _lib.load()
+    rc = lib.fo_flash_attn_bwd(
+        Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(), dO.data_ptr(), LSE.data_ptr(),
+        dQ.data_ptr(), dK.data_ptr(), dV.data_ptr(), dq_accum.data_ptr(), delta.data_ptr(),
+        B, H, M, N, D, _strides3(Q), _strides3(K), _strides3(V), _strides3(O), _strides3(dO),
+        _strides3(dQ), _strides3(dK), _strides3(dV),
+        _lib.dtype_code(Q.dtype), int(bool(causal)), scale, Q.device.index, _lib.current_stream_ptr(Q.device))
+    _lib.check(rc)
+    return dQ, dK, dV
+
+
+class _AttentionFunction(Function):
+    """Forward + backward with the keyword arguments carried as non-tensor inputs."""
+
+    @staticmethod
+    def forward(ctx, Q: Tensor, K: Tensor, V: Tensor, causal: bool, softmax_scale: Optional[float]):
+        O, lse = flash_attention_forward(Q, K, V, causal=causal, softmax_scale=softmax_scale, return_lse=True)
+        ctx.save_for_backward(Q, K, V, O, lse)
+        ctx.causal, ctx.softmax_scale = causal, softmax_scale
+        ctx.mark_non_differentiable(lse)
+        return O, lse
+
+    @staticmethod
+    def backward(ctx, dO: Tensor, _dlse):
+        Q, K, V, O, lse = ctx.saved_tensors
+        if dO.stride(3) != 1:
+            dO = dO.contiguous()
+        dQ, dK, dV = flash_attention_backward(dO, Q, K, V, O, lse, causal=ctx.causal,
+                                              softmax_scale=ctx.softmax_scale)
+        return dQ, dK, dV, None, None
+
+
 class FlashAttentionFunction(Function):
-    """fast_ops/flash_attention/flash_attention.py:28-45: forward only; backward raises."""
+    """fast_ops/flash_attention/flash_attention.py:28-45.  The reference's backward is a
+    placeholder that raises; here it returns (dQ, dK, dV)."""
 
     @staticmethod
     def forward(ctx, Q: Tensor, K: Tensor, V: Tensor) -> Tensor:
-        return flash_attention_forward(Q, K, V)
+        O, lse = flash_attention_forward(Q, K, V, return_lse=True)
+        ctx.save_for_backward(Q, K, V, O, lse)
+        return O
 
     @staticmethod
     def backward(ctx, dO: Tensor):
-        raise NotImplementedError
+        Q, K, V, O, lse = ctx.saved_tensors
+        if dO.stride(3) != 1:
+            dO = dO.contiguous()
+        return flash_attention_backward(dO, Q, K, V, O, lse)
 
 
 def multi_head_attention(Q: Tensor, K: Tensor, V: Tensor, *, causal: bool = False,
@@ -102,4 +170,7 @@ def multi_head_attention(Q: Tensor, K: Tensor, V: Tensor, *, causal: bool = Fals
     """
     if not causal and softmax_scale is None and not return_lse:
         return FlashAttentionFunction.apply(Q, K, V)
+    if torch.is_grad_enabled() and (Q.requires_grad or K.requires_grad or V.requires_grad):
+        O, lse = _AttentionFunction.apply(Q, K, V, bool(causal), softmax_scale)
+        return (O, lse) if return_lse else O
     return flash_attention_forward(Q, K, V, causal=causal, softmax_scale=softmax_scale, return_lse=return_lse)

@@ -71,6 +71,25 @@ int fo_flash_attn_fwd(const void* q, const void* k, const void* v, void* o, floa
                       int device, void* stream);
 
 /*
+ * FlashAttention backward: dQ, dK, dV for the output gradient `dout`, given the forward's inputs,
+ * its output O and its LSE.  The reference's CUDA path leaves backward unimplemented
+ * (fast_ops/flash_attention/flash_attention.py:41-45); the semantics are those of its complete
+ * implementation (fast_ops/flash_attention/flash_attention_triton.py:273-315, :322-638, :832-958).
+ * Layouts, dtypes, D, causal and softmax_scale as in fo_flash_attn_fwd; every tensor has its own
+ * batch/head/sequence strides.  `dq_accum` (B*H*Sq*D floats) and `delta` (B*H*Sq floats) are
+ * scratch the caller provides; their contents on entry do not matter.  Three launches on `stream`:
+ * delta = rowsum(O o dO), the main kernel (dK, dV per key tile; dQ added into dq_accum with
+ * atomics, so dQ may differ in the last bit between runs), and the rounding of dq_accum into dq.
+ */
+int fo_flash_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                      const float* lse, void* dq, void* dk, void* dv, float* dq_accum, float* delta,
+                      int B, int H, int Sq, int Sk, int D,
+                      const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
+                      const int64_t o_strides[3], const int64_t do_strides[3],
+                      const int64_t dq_strides[3], const int64_t dk_strides[3], const int64_t dv_strides[3],
+                      int dtype, int causal, float softmax_scale, int device, void* stream);
+
+/*
  * Fused Lion step on one dense tensor, in place:
  *   p <- p * (1 - lr*wd);  u = sign(beta1*m + (1-beta1)*g);  p <- p - lr*u;
  *   m <- beta2*m + (1-beta2)*g

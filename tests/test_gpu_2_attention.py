@@ -129,9 +129,6 @@ def test_reference_call_signature_and_errors(cuda_device):
     ref, _ = oracle.attention_fwd(q, k, v)
     assert out.dtype == torch.float16 and out.shape == q.shape
     assert (out.cpu().float() - ref).abs().max().item() <= TOL[torch.float16]
-    with pytest.raises(NotImplementedError):  # backward is a placeholder in the reference too
-        o = multi_head_attention(qd.requires_grad_(True), kd, vd)
-        o.sum().backward()
     with pytest.raises(RuntimeError):
         multi_head_attention(qd.float(), kd.float(), vd.float())
     with pytest.raises(RuntimeError):

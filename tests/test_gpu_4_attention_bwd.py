@@ -1,0 +1,95 @@
+"""FlashAttention backward on the GPU against the reference's autograd vectors and the CPU oracle.
+
+The bar is the reference's own (tests/test_flash_attention_triton.py:132-142): the maximum
+absolute error against the fp32 gradients must not exceed twice the error of a plain torch
+implementation running in the same 16-bit precision.
+"""
+import numpy as np
+import pytest
+import torch
+
+import fast_ops_b200._lib as L
+import oracle
+from fast_ops_b200.flash_attention import flash_attention_backward, flash_attention_forward, multi_head_attention
+from helpers import DT, attention_dout, attention_inputs, golden_files, input_digest
+
+pytestmark = pytest.mark.gpu
+
+
+def torch_same_precision_grads(q, k, v, dout, causal):
+    """Attention and its gradients with torch ops in the tensors' own 16-bit dtype."""
+    q, k, v = (t.clone().requires_grad_(True) for t in (q, k, v))
+    d = q.shape[-1]
+    scores = torch.matmul(q, (k / d ** 0.5).transpose(-1, -2))
+    if causal:
+        mask = torch.triu(torch.ones(q.shape[2], k.shape[2], dtype=torch.bool, device=q.device), 1)
+        scores = scores.masked_fill(mask, float("-inf"))
+    out = torch.matmul(torch.softmax(scores, dim=-1), v)
+    out.backward(dout)
+    return q.grad, k.grad, v.grad
+
+
+def run_backward(q, k, v, dout, causal, device):
+    qd, kd, vd, dd = (t.to(device) for t in (q, k, v, dout))
+    o, lse = flash_attention_forward(qd, kd, vd, causal=causal, return_lse=True)
+    dq, dk, dv = flash_attention_backward(dd, qd, kd, vd, o, lse, causal=causal)
+    torch.cuda.synchronize()
+    assert L.device_status(device.index) == 0, "a kernel wait timed out"
+    same = torch_same_precision_grads(qd, kd, vd, dd, causal)
+    return (dq, dk, dv), same
+
+
+def check(got, same, want, what):
+    for name, g, s, w in zip(("dq", "dk", "dv"), got, same, want):
+        err = (g.float().cpu() - w).abs().max().item()
+        err_torch = (s.float().cpu() - w).abs().max().item()
+        assert err <= 2 * err_torch + 1e-4, f"{what} {name}: error {err:.3e} vs same-precision torch {err_torch:.3e}"
+
+
+@pytest.mark.parametrize("path", golden_files("attnbwd"), ids=lambda p: p.split("attnbwd_")[-1][:-4])
+def test_backward_matches_reference_autograd_vectors(cuda_device, path):
+    z = np.load(path)
+    B, H, Sq, Sk, D = (int(x) for x in z["shape"])
+    dt = DT[str(z["dtype"])]
+    q, k, v = attention_inputs(int(z["seed"]), B, H, Sq, Sk, D, dt)
+    dout = attention_dout(int(z["seed"]), B, H, Sq, D, dt)
+    assert input_digest(q, k, v, dout) == str(z["input_sha256"])
+    got, same = run_backward(q, k, v, dout, bool(z["causal"]), cuda_device)
+    check(got, same, [torch.from_numpy(z[n]) for n in ("dq", "dk", "dv")], "reference vectors")
+
+
+@pytest.mark.parametrize("case", [
+    # B, H, Sq, Sk, D, dtype, causal
+    (2, 3, 512, 512, 64, torch.bfloat16, True),
+    (1, 2, 1024, 1024, 128, torch.bfloat16, True),
+    (1, 2, 640, 640, 128, torch.float16, False),
+    (1, 1, 129, 129, 64, torch.float16, True),
+    (1, 2, 77, 513, 128, torch.bfloat16, False),
+    (2, 1, 513, 77, 64, torch.bfloat16, True),
+    (1, 1, 1, 1, 128, torch.bfloat16, True),
+], ids=lambda c: "B%dH%dSq%dSk%dD%d_%s_%s" % (c[0], c[1], c[2], c[3], c[4], str(c[5])[6:], "causal" if c[6] else "full"))
+def test_backward_matches_oracle(cuda_device, case):
+    B, H, Sq, Sk, D, dtype, causal = case
+    q, k, v = attention_inputs(4321 + Sq + Sk, B, H, Sq, Sk, D, dtype)
+    dout = attention_dout(77 + Sq, B, H, Sq, D, dtype)
+    want = oracle.attention_bwd(q, k, v, dout, causal=causal)
+    got, same = run_backward(q, k, v, dout, causal, cuda_device)
+    check(got, same, want, "oracle")
+
+
+def test_autograd_through_the_reference_call(cuda_device):
+    q, k, v = attention_inputs(5, 1, 2, 256, 256, 64, torch.bfloat16)
+    dout = attention_dout(5, 1, 2, 256, 64, torch.bfloat16)
+    want = oracle.attention_bwd(q, k, v, dout, causal=False)
+    qd, kd, vd = (t.to(cuda_device).requires_grad_(True) for t in (q, k, v))
+    out = multi_head_attention(qd, kd, vd)  # three positional tensors, as in the reference
+    out.backward(dout.to(cuda_device))
+    same = torch_same_precision_grads(qd.detach(), kd.detach(), vd.detach(), dout.to(cuda_device), False)
+    check((qd.grad, kd.grad, vd.grad), same, want, "autograd")
+    # keyword form with a causal mask
+    want_c = oracle.attention_bwd(q, k, v, dout, causal=True)
+    for t in (qd, kd, vd):
+        t.grad = None
+    multi_head_attention(qd, kd, vd, causal=True).backward(dout.to(cuda_device))
+    same_c = torch_same_precision_grads(qd.detach(), kd.detach(), vd.detach(), dout.to(cuda_device), True)
+    check((qd.grad, kd.grad, vd.grad), same_c, want_c, "autograd causal")
