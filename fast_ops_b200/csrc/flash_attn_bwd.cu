@@ -66,12 +66,12 @@ attn_bwd_finish_dq_kernel(const float* __restrict__ dq_accum, uint16_t* __restri
 
 template <int D, bool kBf16>
 int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
-               const fo::AttnBwdParams& prm, cudaStream_t stream) {
+               const CUtensorMap& tdq, const fo::AttnBwdParams& prm, cudaStream_t stream) {
   auto kernel = fo::attn_bwd_kernel<D, kBf16>;
   constexpr int smem = fo::BwdConfig<D>::kSmemBytes;
   FO_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   dim3 grid((prm.Sk + fo::kBlockN - 1) / fo::kBlockN, prm.B * prm.H);
-  kernel<<<grid, 192, smem, stream>>>(tq, tk, tv, tdo, prm);
+  kernel<<<grid, 192, smem, stream>>>(tq, tk, tv, tdo, tdq, prm);
   fo::g_launch_count.fetch_add(1, std::memory_order_relaxed);
   FO_CUDA_CHECK(cudaGetLastError());
   return FO_OK;
@@ -125,6 +125,8 @@ extern "C" int fo_flash_attn_bwd(const void* q, const void* k, const void* v, co
   if (int rc = fo::make_tensor_map(&tk, k, dtype, B, H, Sk, D, k_strides, "k")) return rc;
   if (int rc = fo::make_tensor_map(&tv, v, dtype, B, H, Sk, D, v_strides, "v")) return rc;
   if (int rc = fo::make_tensor_map(&tdo, dout, dtype, B, H, Sq, D, do_strides, "dout")) return rc;
+  CUtensorMap tdq;
+  if (int rc = fo::make_dq_accum_map(&tdq, dq_accum, static_cast<int64_t>(B) * H, Sq, D)) return rc;
 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool bf16 = dtype == FO_BF16;
@@ -164,8 +166,8 @@ extern "C" int fo_flash_attn_bwd(const void* q, const void* k, const void* v, co
   prm.scale_log2 = softmax_scale * 1.4426950408889634f;
   prm.device_status = status;
   int rc;
-  if (D == 128) rc = bf16 ? launch_bwd<128, true>(tq, tk, tv, tdo, prm, s) : launch_bwd<128, false>(tq, tk, tv, tdo, prm, s);
-  else rc = bf16 ? launch_bwd<64, true>(tq, tk, tv, tdo, prm, s) : launch_bwd<64, false>(tq, tk, tv, tdo, prm, s);
+  if (D == 128) rc = bf16 ? launch_bwd<128, true>(tq, tk, tv, tdo, tdq, prm, s) : launch_bwd<128, false>(tq, tk, tv, tdo, tdq, prm, s);
+  else rc = bf16 ? launch_bwd<64, true>(tq, tk, tv, tdo, tdq, prm, s) : launch_bwd<64, false>(tq, tk, tv, tdo, tdq, prm, s);
   if (rc) return rc;
 
   {

@@ -5,7 +5,8 @@
 // (fast_ops/flash_attention/flash_attention_triton.py:273-315 for delta = rowsum(O o dO),
 // :322-638 for the main loop): one CTA owns a 128-key tile, keeps dK and dV for it in tensor
 // memory, walks the query tiles that see those keys, and adds its share of dQ into an fp32
-// buffer with atomics (as the reference does, :610).
+// buffer (the reference uses scalar atomics, :610; here each tile goes through shared memory and
+// one tiled bulk reduce-add, cp.reduce.async.bulk.tensor).
 //
 // Per query tile, five tcgen05 MMAs (all fp32 accumulation in tensor memory):
 //   S  = Q K^T          (Q, K K-major from shared memory)
@@ -14,7 +15,7 @@
 //      memory as 16-bit [query row][key] tiles in the 128-byte-swizzled layout --
 //   dV += P^T dO        (P as the M-major A operand, dO as the N-major B operand)
 //   dK += dS^T Q        (dS M-major A, Q N-major B)
-//   dQ  = dS K          (dS K-major A, K N-major B), read back and added to the fp32 dQ buffer
+//   dQ  = dS K          (dS K-major A, K N-major B), read back and reduce-added to the fp32 dQ buffer
 //
 // Warps 0-3: one thread per query row (and per key row in the epilogue); warp 4 issues the MMAs;
 // warp 5 issues the TMA loads.  This first version runs the steps of a query tile in order, with
@@ -72,7 +73,7 @@ template <int D, bool kBf16>
 __global__ void __launch_bounds__(192, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
-                const AttnBwdParams prm) {
+                const __grid_constant__ CUtensorMap tm_dq, const AttnBwdParams prm) {
   using Cfg = BwdConfig<D>;
   constexpr int kTileBytes = Cfg::kTileBytes;
   constexpr int kBoxes = D / kBoxCols;
@@ -127,6 +128,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     prefetch_tensormap(&tm_k);
     prefetch_tensormap(&tm_v);
     prefetch_tensormap(&tm_do);
+    prefetch_tensormap(&tm_dq);
   }
   __syncthreads();
   if (*skip) return;
@@ -155,6 +157,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const bool need_mask = (k0 + kBlockN > prm.Sk) || (prm.causal && k0 + kBlockN - 1 > q0);
       mbar_wait(bar_s_full, it & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_MMA);
       tcgen05_fence_after_sync();
+      // the P / dS buffers double as the staging area of the previous tile's dQ reduction: its
+      // shared-memory reads must have finished before they are overwritten
+      if (it > 0) {
+        if (tid == 0) tma_store_wait_read();
+        named_barrier_sync(1, 128);
+      }
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t sr[32], dpr[32];
@@ -191,20 +199,30 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       // dQ tile of this (query tile, key tile) pair -> fp32 accumulation buffer
       mbar_wait(bar_dq_full, it & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_MMA);
       tcgen05_fence_after_sync();
-      float* dq_row = prm.dq_accum + (static_cast<int64_t>(bh) * prm.Sq + row) * D;
+      // stage the fp32 tile in shared memory (over P and dS, which the MMAs have finished
+      // reading) as D/32 swizzled boxes of [128 rows x 32 floats], then add it into the global
+      // accumulation buffer with tiled bulk reductions; rows past Sq are dropped by the hardware
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
         uint32_t qr[32];
         tmem_ld32(tS + c * 32, qr);
         tmem_ld_wait(qr);
-        if (row_ok) {
 #pragma unroll
-          for (int x = 0; x < 32; ++x) atomicAdd(dq_row + c * 32 + x, __uint_as_float(qr[x]));
-        }
+        for (int u = 0; u < 8; ++u)
+          *reinterpret_cast<uint4*>(sP + c * kBoxBytes + tid * 128 + ((u ^ (tid & 7)) * 16)) =
+              make_uint4(qr[4 * u], qr[4 * u + 1], qr[4 * u + 2], qr[4 * u + 3]);
       }
+      fence_proxy_async_smem();
       tcgen05_fence_before_sync();
       mbar_arrive(bar_s_free);
+      named_barrier_sync(1, 128);
+      if (tid == 0) {
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) tma_reduce_add_3d(&tm_dq, sP + c * kBoxBytes, c * 32, q0, bh);
+        tma_store_commit();
+      }
     }
+    if (tid == 0) tma_store_wait_all();  // the reductions must have landed before the CTA ends
 
     // ---- epilogue: dK, dV of key row (k0 + tid) ----
     const int kv_row = k0 + tid;
@@ -281,12 +299,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
       for (int kk = 0; kk < kBlockM / 16; ++kk)  // dK += dS^T Q
         umma_ss_lo_elect(tDK, ds_m + kk * 128, q_n + kk * 128, idesc_t, (it > 0 || kk > 0) ? 1u : 0u);
+      // Q_i and dO_i have no reader after this point: let the next tile's load start under dQ
+      tcgen05_commit_elect(bar_q_empty);
 #pragma unroll
       for (int kk = 0; kk < kBlockN / 16; ++kk) {  // dQ = dS K  (K = 16 keys per step), over the S columns
         const uint32_t off = (kk >> 2) * kBoxStep + (kk & 3) * 2;
         umma_ss_lo_elect(tS, ds_k + off, k_n + kk * 128, idesc_q, kk > 0 ? 1u : 0u);
       }
-      tcgen05_commit_elect(bar_q_empty);
       tcgen05_commit_elect(bar_dq_full);
     }
   } else {

@@ -57,4 +57,20 @@ inline int make_tensor_map(CUtensorMap* map, const void* base, int dtype, int B,
   return FO_OK;
 }
 
+// Tensor map over the fp32 dQ accumulation buffer (B*H, Sq, D), dense: box = 128 rows x 32
+// floats (128 bytes, one swizzle span), used as the destination of tiled reduce-adds.
+inline int make_dq_accum_map(CUtensorMap* map, float* base, int64_t BH, int Sq, int D) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fo::fail(FO_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(Sq), static_cast<cuuint64_t>(BH)};
+  const cuuint64_t gstrides[2] = {static_cast<cuuint64_t>(D) * 4, static_cast<cuuint64_t>(Sq) * D * 4};
+  const cuuint32_t box[3] = {32, kBlockM, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, base, dims, gstrides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fo::fail(FO_ERR_CUDA, "cuTensorMapEncodeTiled(dq_accum) failed with CUresult %d", (int)r);
+  return FO_OK;
+}
+
 }  // namespace fo
