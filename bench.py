@@ -13,7 +13,8 @@ step on the GPT-2-medium list and, sharded ZeRO-1 style, on the Llama-7B list).
 `cpu_baseline` times the CPU oracle (a C restatement of the reference's torch code) on a
 bounded sample of the same workload.  `--impl reference` runs only that CPU arm.
 
-Workloads: attn_c3 (default), attn_c2, lion_c4, lion_c5.
+Workloads: attn_c3 (default), attn_c2, attn_bwd_c3, lion_c4, lion_c5 (attn_prof and attn_bwd_prof are
+the small shapes used for profiler captures).
 Launch under torchrun for N > 1 (one rank per GPU); inputs are synthetic and seeded.
 """
 from __future__ import annotations
@@ -262,6 +263,31 @@ def bench_attention(d: Dist, name: str, steps: int, warmup: int, peaks, with_e2e
     return out
 
 
+def bench_attention_bwd(d: Dist, name: str, steps: int, warmup: int, peaks):
+    """Backward of the same attention shape: dQ, dK, dV from dO (three launches per step: delta,
+    the main kernel, the rounding of dQ).  FLOPs = 2.5 x the forward's (five matmuls against two)."""
+    import fast_ops_b200._lib as L
+    from fast_ops_b200.flash_attention import flash_attention_backward, flash_attention_forward
+
+    B, H, S, D, causal = ATTN[name]
+    q, k, v = attn_inputs(B, H, S, D, d.device, seed=2000 + d.rank)
+    dout = attn_inputs(B, H, S, D, d.device, seed=3000 + d.rank)[0]
+    o, lse = flash_attention_forward(q, k, v, causal=causal, return_lse=True)
+    lib = L.load()
+    l0 = lib.fo_launch_count()
+    ms, _ = timed_steps(d, lambda: flash_attention_backward(dout, q, k, v, o, lse, causal=causal), steps, warmup)
+    launches = lib.fo_launch_count() - l0 - 3 * warmup
+    if L.device_status(d.local_rank) != 0:
+        raise RuntimeError("an attention kernel reported a timed-out wait")
+    flops = 2.5 * attn_flops(B, H, S, D, causal)
+    tf = flops / (ms * 1e-3) / 1e12
+    return {"workload": f"{name} backward: dQ, dK, dV for B={B} H={H} S={S} D={D} bf16 causal={causal}, per GPU",
+            "value": tf * d.world, "unit": "TFLOP/s", "ms_per_step": ms, "gpu_launches": launches,
+            "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                         "frac": tf / peaks["bf16_tflops"], "traffic": None,
+                         "peak_source": peaks["source"] + " cuBLAS bf16 burst"}}
+
+
 def cpu_attention_sample(name: str, row_stride: int, reps: int):
     """Times the CPU oracle on one (batch, head) slice of the workload, every `row_stride`-th
     query row (the causal row costs are sampled evenly), all host threads."""
@@ -481,7 +507,8 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default="attn_c3", choices=["attn_c3", "attn_c2", "attn_prof", "lion_c4", "lion_c5"])
+    ap.add_argument("--workload", default="attn_c3",
+                    choices=["attn_c3", "attn_c2", "attn_prof", "attn_bwd_c3", "attn_bwd_prof", "lion_c4", "lion_c5"])
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-also", action="store_true", help="skip the secondary workloads")
@@ -499,7 +526,12 @@ def main():
     d = Dist(args.gpus)
     line = {"n_gpus": d.world, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True,
             "vs_baseline": None, "data": "synthetic"}
-    if args.workload.startswith("attn"):
+    if args.workload.startswith("attn_bwd"):
+        r = bench_attention_bwd(d, args.workload.replace("_bwd", ""), args.steps, args.warmup, peaks)
+        line.update({"metric": "attention_bwd_tflops", "scaling": "weak", "dtype": "bf16",
+                     "config": {"workload": r.pop("workload"), "l2": "inputs larger than L2"}})
+        line.update(r)
+    elif args.workload.startswith("attn"):
         r = bench_attention(d, args.workload, args.steps, args.warmup, peaks, with_e2e=not args.no_e2e)
         line.update({"metric": "attention_fwd_tflops", "unit": "TFLOP/s", "scaling": "weak", "dtype": "bf16"})
         line.update(r)
@@ -520,6 +552,8 @@ def main():
             a = bench_attention(d, "attn_c2", max(args.steps, 50), args.warmup, peaks, with_e2e=False, with_clocks=False)
             also["attn_c2"] = {k: a[k] for k in ("value", "ms_per_step", "roofline", "config")}
             also["attn_c2"]["unit"] = "TFLOP/s"
+        if not args.workload.startswith("attn_bwd"):
+            also["attn_bwd_c3"] = bench_attention_bwd(d, "attn_c3", max(3, args.steps // 4), 2, peaks)
         if args.workload != "lion_c4":
             also["lion_c4"] = bench_lion_c4(d, args.steps, args.warmup, peaks)
         if args.workload != "lion_c5":
@@ -527,7 +561,9 @@ def main():
         line["also"] = also
 
     if d.rank == 0 and d.world == 1 and not args.no_cpu:
-        if args.workload.startswith("attn"):
+        if args.workload.startswith("attn_bwd"):
+            pass
+        elif args.workload.startswith("attn"):
             line["cpu_baseline"], _ = cpu_attention_sample(args.workload, 1, 3)
             if not args.no_also:
                 line["also"]["lion_c4"]["cpu_baseline"] = cpu_lion_sample(3)
