@@ -24,6 +24,7 @@ struct AttnParams {
   int* device_status;
   int num_q_tiles;
   int head_group;  // heads per scheduling group (>= 1)
+  int kv_head_bcast;  // 1: K and V have one head shared by all query heads (multi-query attention)
   // Optional timeline of CTA 0 (debug): [role][key tile][event] SM clock values, or null.
   unsigned long long* trace;
 };

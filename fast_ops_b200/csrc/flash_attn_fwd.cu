@@ -180,8 +180,15 @@ extern "C" int fo_flash_attn_fwd(const void* q, const void* k, const void* v, vo
 
   CUtensorMap tq, tk, tv;
   if (int rc = make_tensor_map(&tq, q, dtype, B, H, Sq, D, q_strides, "q")) return rc;
-  if (int rc = make_tensor_map(&tk, k, dtype, B, H, Sk, D, k_strides, "k")) return rc;
-  if (int rc = make_tensor_map(&tv, v, dtype, B, H, Sk, D, v_strides, "v")) return rc;
+  // Multi-query attention: K and V expanded over the head dimension with stride 0 (one shared
+  // head, as the reference's tests build it, tests/test_flash_attention_triton.py:71-73) are
+  // described to TMA as single-head tensors and every query head reads head 0.
+  const bool kv_bcast = H > 1 && k_strides[1] == 0 && v_strides[1] == 0;
+  FO_REQUIRE(kv_bcast || H == 1 || (k_strides[1] != 0 && v_strides[1] != 0),
+             "k and v must both have a head stride, or both be expanded with head stride 0");
+  const int Hkv = kv_bcast ? 1 : H;
+  if (int rc = make_tensor_map(&tk, k, dtype, B, Hkv, Sk, D, k_strides, "k")) return rc;
+  if (int rc = make_tensor_map(&tv, v, dtype, B, Hkv, Sk, D, v_strides, "v")) return rc;
 
   AttnParams prm;
   prm.o = o;
@@ -198,6 +205,7 @@ extern "C" int fo_flash_attn_fwd(const void* q, const void* k, const void* v, vo
   prm.device_status = status;
   prm.num_q_tiles = (Sq + kBlockM - 1) / kBlockM;
   prm.trace = g_attn_trace;
+  prm.kv_head_bcast = kv_bcast ? 1 : 0;
   {
     // as many heads per group as keep their K and V (2 * Sk * D * 2 bytes each) within about a
     // third of the 126 MB L2, leaving room for Q, O and the other traffic

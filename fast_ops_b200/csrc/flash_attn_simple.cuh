@@ -44,6 +44,7 @@ attn_fwd_simple_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   const int bh = blockIdx.y;
   const int b = bh / prm.H;
   const int h = bh - b * prm.H;
+  const int hk = prm.kv_head_bcast ? 0 : h;  // head coordinate of K and V
   const int q0 = q_tile * kBlockM;
 
   if (tid == 0) {
@@ -96,8 +97,8 @@ attn_fwd_simple_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     const int k0 = j * kBlockN;
     if (tid == 0) {
       mbar_arrive_expect_tx(bar_kv, 2 * kTileBytes);
-      for (int c = 0; c < kBoxes; ++c) tma_load_4d(sK + c * kBoxBytes, &tm_k, bar_kv, c * kBoxCols, k0, h, b);
-      for (int c = 0; c < kBoxes; ++c) tma_load_4d(sV + c * kBoxBytes, &tm_v, bar_kv, c * kBoxCols, k0, h, b);
+      for (int c = 0; c < kBoxes; ++c) tma_load_4d(sK + c * kBoxBytes, &tm_k, bar_kv, c * kBoxCols, k0, hk, b);
+      for (int c = 0; c < kBoxes; ++c) tma_load_4d(sV + c * kBoxBytes, &tm_v, bar_kv, c * kBoxCols, k0, hk, b);
     }
     mbar_wait(bar_kv, phase_kv, cta_abort, prm.device_status, FO_STATUS_TIMEOUT_TMA);
     phase_kv ^= 1;

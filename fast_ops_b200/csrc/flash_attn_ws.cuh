@@ -109,6 +109,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   const int bh = group * prm.head_group + in_group % heads_here;
   const int b = bh / prm.H;
   const int h = bh - b * prm.H;
+  const int hk = prm.kv_head_bcast ? 0 : h;  // head coordinate of K and V
   const int n_kv_total = (prm.Sk + kBlockN - 1) / kBlockN;
   // key tiles visited by query tile 0 / 1 of this pair; n1 >= n0 >= 1
   const int n0 = prm.causal ? min(n_kv_total, 2 * pair + 1) : n_kv_total;
@@ -421,7 +422,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           const CUtensorMap* map = (i & 1) ? &tm_v : &tm_k;
           for (int c = 0; c < kBoxes; ++c)
             tma_load_4d(sKV + st * kTileBytes + c * kBoxBytes, map, bar_kv_full + st, c * kBoxCols,
-                        (i >> 1) * kBlockN, h, b);
+                        (i >> 1) * kBlockN, hk, b);
         }
         __syncwarp();
       }

@@ -33,7 +33,9 @@ def flash_attention_forward(Q: Tensor, K: Tensor, V: Tensor, *, causal: bool = F
 
     Q: (B, H, M, D); K, V: (B, H, N, D); fp16 or bf16; D in {64, 128}; the last dimension
     contiguous, the others with strides that are multiples of 8 elements (so (B, S, H, D)
-    tensors viewed as (B, H, S, D) are accepted without a copy).  Returns O (B, H, M, D) in
+    tensors viewed as (B, H, S, D) are accepted without a copy).  K and V may be expanded over the
+    head dimension (stride 0: multi-query attention); the shared head is then read once per tile
+    from the single copy.  Returns O (B, H, M, D) in
     Q's dtype, plus LSE (B, H, M) fp32 when `return_lse`.  `out`, if given, receives O: shape
     (B, H, M, D), Q's dtype and device, last dimension contiguous (any layout otherwise).
     """
@@ -100,6 +102,10 @@ def flash_attention_backward(dO: Tensor, Q: Tensor, K: Tensor, V: Tensor, O: Ten
     if LSE.shape != (B, H, M) or LSE.dtype != torch.float32 or not LSE.is_contiguous() or LSE.device != Q.device:
         raise RuntimeError("LSE must be a contiguous (B, H, M) float32 tensor on Q's device")
     scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(D)
+    if K.stride(1) == 0 or V.stride(1) == 0:
+        # multi-query K/V expanded over the heads: the kernel writes one dK, dV per query head
+        # (autograd sums them through the expand), so it needs per-head storage to read from too
+        K, V = K.contiguous(), V.contiguous()
     dQ, dK, dV = torch.empty_like(Q), torch.empty_like(K), torch.empty_like(V)
     for t in (dQ, dK, dV):
         if t.stride(3) != 1:

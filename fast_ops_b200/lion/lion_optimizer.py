@@ -16,6 +16,9 @@ Keyword-only extensions:
   fused_gather     with process_group: the flat parameter buffer is a symmetric-memory
                    allocation and the step kernel itself stores the updated slice into every
                    peer's buffer over NVLink, replacing the all-gather.
+  reduce_gradients with process_group: step() first averages the flat gradient buffer across
+                   the ranks with one reduce-scatter into this rank's slice (otherwise the caller
+                   is expected to have reduced the gradients already).
 """
 from __future__ import annotations
 
@@ -116,7 +119,7 @@ class Lion(Optimizer):
 
     def __init__(self, params: Iterable, lr: float = 1e-4, betas: Tuple[float, float] = (0.9, 0.99),
                  weight_decay: float = 0.0, *, momentum_dtype: Optional[torch.dtype] = None,
-                 process_group=None, fused_gather: bool = False) -> None:
+                 process_group=None, fused_gather: bool = False, reduce_gradients: bool = False) -> None:
         if lr <= 0:
             raise RuntimeError(f"expected positive LR, got {lr}")
         if not all(0 <= beta <= 1 for beta in betas):
@@ -131,8 +134,10 @@ class Lion(Optimizer):
         self._zero = None
         if fused_gather and process_group is None:
             raise RuntimeError("fused_gather needs a process_group")
+        if reduce_gradients and process_group is None:
+            raise RuntimeError("reduce_gradients needs a process_group")
         if process_group is not None:
-            self._zero = _Zero1State(self, process_group, momentum_dtype, fused_gather)
+            self._zero = _Zero1State(self, process_group, momentum_dtype, fused_gather, reduce_gradients)
 
     # -- multi-tensor path ---------------------------------------------------------------
     @torch.no_grad()
@@ -176,6 +181,13 @@ class Lion(Optimizer):
                     float(lr), float(beta1), float(beta2), float(weight_decay), device_index,
                     _lib.current_stream_ptr(torch.device("cuda", device_index))))
 
+    def load_state_dict(self, state_dict) -> None:
+        """As torch.optim.Optimizer.load_state_dict; in process_group mode the loaded momentum
+        (this rank's slices, as state_dict() saved them) is copied back into the rank's shard."""
+        super().load_state_dict(state_dict)
+        if self._zero is not None:
+            self._zero.adopt_loaded_state()
+
     # -- ZeRO-1 accessors ------------------------------------------------------------------
     @property
     def flat_params(self) -> Optional[Tensor]:
@@ -196,9 +208,11 @@ class _Zero1State:
     the all-gather of updated weights.
     """
 
-    def __init__(self, opt: Lion, group, momentum_dtype: Optional[torch.dtype], fused_gather: bool = False):
+    def __init__(self, opt: Lion, group, momentum_dtype: Optional[torch.dtype], fused_gather: bool = False,
+                 reduce_gradients: bool = False):
         import torch.distributed as dist
 
+        self.reduce_gradients = reduce_gradients
         self.opt = opt
         self.group = group
         self.world = dist.get_world_size(group)
@@ -246,7 +260,30 @@ class _Zero1State:
             _, s0, n = self.layout.tensor_slice_in_shard(i, self.rank)
             opt.state[p]["exp_avg"] = self.m_shard[s0:s0 + n]
         self.flat_step_fn = _flat_step
-        self.last_step_ms = None
+
+    def adopt_loaded_state(self) -> None:
+        """After Optimizer.load_state_dict: state[p]["exp_avg"] holds fresh tensors; copy them
+        into the shard and point the state back at views of it."""
+        with torch.no_grad():
+            for i, p in enumerate(self.params):
+                _, s0, n = self.layout.tensor_slice_in_shard(i, self.rank)
+                view = self.m_shard[s0:s0 + n]
+                loaded = self.opt.state[p].get("exp_avg")
+                if loaded is not None and loaded.data_ptr() != view.data_ptr():
+                    if loaded.numel() != n:
+                        raise RuntimeError("loaded exp_avg does not match this rank's slice of the parameter")
+                    view.copy_(loaded.reshape(-1))
+                self.opt.state[p]["exp_avg"] = view
+
+    def _average_gradients(self) -> None:
+        import torch.distributed as dist
+
+        shard = self.flat_g[self.begin:self.end]
+        if dist.get_backend(self.group) == "gloo":  # no reduce-scatter there: all-reduce, keep the slice
+            dist.all_reduce(self.flat_g, group=self.group)
+            shard.div_(self.world)
+        else:
+            dist.reduce_scatter_tensor(shard, self.flat_g, op=dist.ReduceOp.AVG, group=self.group)
 
     @torch.no_grad()
     def step(self) -> None:
@@ -258,6 +295,8 @@ class _Zero1State:
             if p.grad.data_ptr() != gview.data_ptr():
                 gview.copy_(p.grad)
                 p.grad = gview
+        if self.reduce_gradients and self.world > 1:
+            self._average_gradients()
         group = self.opt.param_groups[0]
         if self.symm is not None:
             # ranks meet before any of them overwrites a peer's weights, and again before any of

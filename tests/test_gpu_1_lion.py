@@ -147,3 +147,35 @@ def test_lion_interface_and_errors(cuda_device):
     with pytest.raises(RuntimeError):  # non-dense
         big = torch.zeros(32, device=cuda_device, dtype=torch.bfloat16)
         lion_update(big[::2], big[::2], big[::2], 1e-2, 0.9, 0.99, 0.0)
+
+
+def test_lion_step_replays_from_a_cuda_graph(cuda_device):
+    """The multi-tensor step allocates nothing once its table is cached, so it can be captured."""
+    gen = torch.Generator().manual_seed(9)
+    shapes = [(300, 40), (5000,), (17,)]
+    cpu_p = [(torch.randn(s, generator=gen) * 0.02).bfloat16() for s in shapes]
+    cpu_m = [torch.zeros(s, dtype=torch.bfloat16) for s in shapes]
+    params = [t.clone().to(cuda_device).requires_grad_(True) for t in cpu_p]
+    for p in params:
+        p.grad = torch.zeros_like(p)
+    opt = Lion(params, lr=1e-3, weight_decay=0.1)
+    grads = [[(torch.randn(s, generator=gen) * 1e-3).bfloat16() for s in shapes] for _ in range(3)]
+
+    def load(step):
+        for p, g in zip(params, grads[step]):
+            p.grad.copy_(g.to(cuda_device))
+
+    load(0)
+    opt.step()  # eager: builds and caches the device table
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):  # recorded, not run
+        opt.step()
+    for step in (1, 2):
+        load(step)
+        graph.replay()
+    torch.cuda.synchronize()
+    for step in range(3):
+        for cp, g, cm in zip(cpu_p, grads[step], cpu_m):
+            oracle.lion_step(cp, g, cm, 1e-3, (0.9, 0.99), 0.1)
+    for p, cp, cm in zip(params, cpu_p, cpu_m):
+        assert torch.equal(p.detach().cpu(), cp) and torch.equal(opt.state[p]["exp_avg"].cpu(), cm)

@@ -157,3 +157,19 @@ def test_host_pipelined_forward_matches_device_forward(cuda_device):
     assert torch.equal(host_out2, host_out)
     with pytest.raises(RuntimeError):
         flash_attention_forward_host(q.to(cuda_device), hk, hv)
+
+
+def test_multi_query_expanded_kv(cuda_device, impl):
+    """K and V with one head expanded over H query heads (stride 0), as the reference's tests
+    build multi-query inputs (tests/test_flash_attention_triton.py:71-73)."""
+    B, H, S, D = 2, 4, 300, 128
+    gen = torch.Generator().manual_seed(31)
+    q = torch.randn(B, H, S, D, generator=gen).bfloat16()
+    k1, v1 = (torch.randn(B, 1, S, D, generator=gen).bfloat16() for _ in range(2))
+    ref, ref_lse = oracle.attention_fwd(q, k1.expand(B, H, S, D), v1.expand(B, H, S, D), causal=True)
+    kd, vd = k1.to(cuda_device).expand(B, H, S, D), v1.to(cuda_device).expand(B, H, S, D)
+    assert kd.stride(1) == 0
+    out, lse = flash_attention_forward(q.to(cuda_device), kd, vd, causal=True, return_lse=True)
+    torch.cuda.synchronize()
+    assert (out.cpu().float() - ref).abs().max().item() <= TOL[torch.bfloat16]
+    assert (lse.cpu() - ref_lse).abs().max().item() <= LSE_TOL

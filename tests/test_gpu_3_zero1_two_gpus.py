@@ -21,7 +21,7 @@ def _free_port():
     return port
 
 
-def _worker(rank, world, port, fused, ret):
+def _worker(rank, world, port, fused, reduce, ret):
     sys.path.insert(0, ROOT)
     import torch.distributed as dist
 
@@ -39,13 +39,14 @@ def _worker(rank, world, port, fused, ret):
         init = [(torch.randn(s, generator=gen) * 0.02).bfloat16() for s in shapes]
         params = [t.clone().to(dev).requires_grad_(True) for t in init]
         opt = Lion(params, lr=1e-3, betas=(0.9, 0.99), weight_decay=0.1, process_group=dist.group.WORLD,
-                   fused_gather=fused)
+                   fused_gather=fused, reduce_gradients=reduce)
         ref_p = [t.clone() for t in init]
         ref_m = [torch.zeros_like(t) for t in init]
         for step in range(3):
             grads = [(torch.randn(s, generator=gen) * 1e-3).bfloat16() for s in shapes]
             for p, g in zip(params, grads):
-                p.grad.copy_(g.to(dev))
+                # with reduce_gradients the ranks hold g/2 and 3g/2, whose average is g exactly
+                p.grad.copy_((g * (1.0 if not reduce else (0.5 if rank == 0 else 1.5))).to(dev))
             opt.step()
             for rp, g, rm in zip(ref_p, grads, ref_m):
                 oracle.lion_step(rp.view(-1), g.view(-1), rm.view(-1), 1e-3, (0.9, 0.99), 0.1)
@@ -57,11 +58,12 @@ def _worker(rank, world, port, fused, ret):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("fused", [False, True], ids=["nccl_all_gather", "fused_peer_stores"])
-def test_zero1_two_gpus(fused):
+@pytest.mark.parametrize("fused,reduce", [(False, False), (True, False), (False, True)],
+                         ids=["nccl_all_gather", "fused_peer_stores", "reduce_scatter_then_all_gather"])
+def test_zero1_two_gpus(fused, reduce):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     mgr = mp.Manager()
     ret = mgr.dict()
-    mp.spawn(_worker, args=(2, _free_port(), fused, ret), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, _free_port(), fused, reduce, ret), nprocs=2, join=True)
     assert dict(ret) == {0: "ok", 1: "ok"}

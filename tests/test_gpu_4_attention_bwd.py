@@ -93,3 +93,19 @@ def test_autograd_through_the_reference_call(cuda_device):
     multi_head_attention(qd, kd, vd, causal=True).backward(dout.to(cuda_device))
     same_c = torch_same_precision_grads(qd.detach(), kd.detach(), vd.detach(), dout.to(cuda_device), True)
     check((qd.grad, kd.grad, vd.grad), same_c, want_c, "autograd causal")
+
+
+def test_backward_multi_query_sums_over_heads(cuda_device):
+    B, H, S, D = 1, 4, 256, 64
+    gen = torch.Generator().manual_seed(41)
+    q = torch.randn(B, H, S, D, generator=gen).bfloat16()
+    k1, v1 = (torch.randn(B, 1, S, D, generator=gen).bfloat16() for _ in range(2))
+    dout = torch.randn(B, H, S, D, generator=gen).bfloat16()
+    dq, dk, dv = oracle.attention_bwd(q, k1.expand(B, H, S, D), v1.expand(B, H, S, D), dout, causal=True)
+    want = (dq, dk.sum(1, keepdim=True), dv.sum(1, keepdim=True))
+    qd, kd, vd = (t.to(cuda_device).requires_grad_(True) for t in (q, k1, v1))
+    out = multi_head_attention(qd, kd.expand(B, H, S, D), vd.expand(B, H, S, D), causal=True)
+    out.backward(dout.to(cuda_device))
+    for name, g, w in zip(("dq", "dk", "dv"), (qd.grad, kd.grad, vd.grad), want):
+        err = (g.float().cpu() - w).abs().max().item()
+        assert err <= 0.03 * max(1.0, w.abs().max().item()), f"{name}: {err}"

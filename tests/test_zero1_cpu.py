@@ -97,6 +97,30 @@ def _worker(rank, world, port, ret):
             t0, s0, n = zero.layout.tensor_slice_in_shard(i, rank)
             assert torch.equal(opt.state[p]["exp_avg"], rm.view(-1)[t0:t0 + n])
         assert all(p.data.data_ptr() >= zero.flat_p.data_ptr() for p in params)
+
+        # state_dict round trip: a fresh optimizer over the same parameters adopts the saved shard
+        sd = opt.state_dict()
+        opt2 = Lion(params, lr=1e-3, betas=(0.9, 0.99), weight_decay=0.1, process_group=dist.group.WORLD)
+        opt2.load_state_dict(sd)
+        assert torch.equal(opt2._zero.m_shard, zero.m_shard)
+        assert all(opt2.state[p]["exp_avg"].data_ptr() >= opt2._zero.m_shard.data_ptr() for p in params
+                   if opt2.state[p]["exp_avg"].numel())
+
+        # reduce_gradients: ranks hold g*(rank+1); the average over two ranks is 1.5*g, taken
+        # here with g scaled so that every value stays exactly representable
+        opt3 = Lion(params, lr=1e-3, betas=(0.9, 0.99), weight_decay=0.1, process_group=dist.group.WORLD,
+                    reduce_gradients=True)
+        opt3._zero.flat_step_fn = cpu_flat_step
+        base = [(torch.randn(s, generator=gen) * 1e-3).bfloat16() for s in shapes]
+        ref_p3 = [p.data.clone() for p in params]
+        ref_m3 = [torch.zeros_like(t) for t in init]
+        for p, g in zip(params, base):
+            p.grad.copy_(g * (2.0 if rank == 0 else 6.0))  # average = 4*g, exact in bf16
+        opt3.step()
+        for rp, g, rm in zip(ref_p3, base, ref_m3):
+            oracle.lion_step(rp.view(-1), (g * 4.0).view(-1), rm.view(-1), 1e-3, (0.9, 0.99), 0.1)
+        for p, rp in zip(params, ref_p3):
+            assert torch.equal(p.data, rp), f"rank {rank}: reduce_gradients step differs"
         ret[rank] = "ok"
     finally:
         dist.destroy_process_group()
