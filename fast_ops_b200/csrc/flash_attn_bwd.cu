@@ -71,7 +71,7 @@ int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& 
   constexpr int smem = fo::BwdConfig<D>::kSmemBytes;
   FO_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   dim3 grid((prm.Sk + fo::kBlockN - 1) / fo::kBlockN, prm.B * prm.H);
-  kernel<<<grid, 192, smem, stream>>>(tq, tk, tv, tdo, tdq, prm);
+  kernel<<<grid, 320, smem, stream>>>(tq, tk, tv, tdo, tdq, prm);
   fo::g_launch_count.fetch_add(1, std::memory_order_relaxed);
   FO_CUDA_CHECK(cudaGetLastError());
   return FO_OK;

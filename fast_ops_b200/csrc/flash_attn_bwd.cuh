@@ -17,8 +17,9 @@
 //   dK += dS^T Q        (dS M-major A, Q N-major B)
 //   dQ  = dS K          (dS K-major A, K N-major B), read back and reduce-added to the fp32 dQ buffer
 //
-// Warps 0-3: one thread per query row (and per key row in the epilogue); warp 4 issues the MMAs;
-// warp 5 issues the TMA loads.  This first version runs the steps of a query tile in order, with
+// Warps 0-7: two threads per query row, each taking half of the tile's columns (no reduction
+// across a row is needed in the backward), and in the epilogue one thread per key row for dK
+// (warps 0-3) and dV (warps 4-7); warp 8 issues the MMAs; warp 9 issues the TMA loads.  This first version runs the steps of a query tile in order, with
 // no overlap between tiles.
 #pragma once
 
@@ -68,9 +69,9 @@ __device__ __forceinline__ void store_swizzled_unit(uint8_t* tile, int r, int u,
   *reinterpret_cast<uint4*>(tile + box * kBoxBytes + r * 128 + slot * 16) = v;
 }
 
-// grid = (key tiles, B*H); block = 192.
+// grid = (key tiles, B*H); block = 320.
 template <int D, bool kBf16>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
                 const __grid_constant__ CUtensorMap tm_dq, const AttnBwdParams prm) {
@@ -91,9 +92,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint64_t* bar_q_full = bars + 1;    // TMA -> MMA: Q_i and dO_i loaded
   uint64_t* bar_q_empty = bars + 2;   // MMA -> TMA: every MMA reading Q_i / dO_i has completed
   uint64_t* bar_s_full = bars + 3;    // MMA -> threads: S and dP are in tensor memory
-  uint64_t* bar_pds_full = bars + 4;  // threads -> MMA: P and dS are in shared memory (128 arrivals)
+  uint64_t* bar_pds_full = bars + 4;  // threads -> MMA: P and dS are in shared memory (256 arrivals)
   uint64_t* bar_dq_full = bars + 5;   // MMA -> threads: dQ tile (and dK, dV so far) complete
-  uint64_t* bar_s_free = bars + 6;    // threads -> MMA: dQ read, S / dP columns reusable (128 arrivals)
+  uint64_t* bar_s_free = bars + 6;    // threads -> MMA: dQ read, S / dP columns reusable (256 arrivals)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::kOffMisc);
   volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* skip = cta_abort + 1;
@@ -120,9 +121,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     mbar_init(bar_q_full, 1);
     mbar_init(bar_q_empty, 1);
     mbar_init(bar_s_full, 1);
-    mbar_init(bar_pds_full, 128);
+    mbar_init(bar_pds_full, 256);
     mbar_init(bar_dq_full, 1);
-    mbar_init(bar_s_free, 128);
+    mbar_init(bar_s_free, 256);
     fence_mbar_init();
     prefetch_tensormap(&tm_q);
     prefetch_tensormap(&tm_k);
@@ -132,7 +133,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   }
   __syncthreads();
   if (*skip) return;
-  if (warp == 4) {
+  if (warp == 8) {
     tmem_alloc(tmem_slot, Cfg::kTmemCols);
     tmem_relinquish_alloc_permit();
   }
@@ -141,15 +142,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   tcgen05_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp < 4) {
+  if (warp < 8) {
     // ================================ compute threads ================================
-    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    const int r = (warp & 3) * 32 + lane;  // row of the tile (tensor-memory lane)
+    const int half = warp >> 2;            // which half of the columns this thread takes
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tS = tmem_base + Cfg::kColS + lane_base;
     const uint32_t tDP = tmem_base + Cfg::kColDP + lane_base;
     for (int it = 0; it < n_iter; ++it) {
       const int i = i0 + it;
       const int q0 = i * kBlockM;
-      const int row = q0 + tid;
+      const int row = q0 + r;
       const bool row_ok = row < prm.Sq;
       // a row past the end gets LSE = +inf, so its P and dS are exactly 0
       const float lse2 = row_ok ? prm.lse[static_cast<int64_t>(bh) * prm.Sq + row] * 1.4426950408889634f : INFINITY;
@@ -161,10 +164,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       // shared-memory reads must have finished before they are overwritten
       if (it > 0) {
         if (tid == 0) tma_store_wait_read();
-        named_barrier_sync(1, 128);
+        named_barrier_sync(1, 256);
       }
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = half * 2 + cc;
         uint32_t sr[32], dpr[32];
         tmem_ld32(tS + c * 32, sr);
         tmem_ld32(tDP + c * 32, dpr);
@@ -187,8 +191,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-          store_swizzled_unit(sP, tid, c * 4 + u, make_uint4(pp[4 * u], pp[4 * u + 1], pp[4 * u + 2], pp[4 * u + 3]));
-          store_swizzled_unit(sDS, tid, c * 4 + u, make_uint4(dd[4 * u], dd[4 * u + 1], dd[4 * u + 2], dd[4 * u + 3]));
+          store_swizzled_unit(sP, r, c * 4 + u, make_uint4(pp[4 * u], pp[4 * u + 1], pp[4 * u + 2], pp[4 * u + 3]));
+          store_swizzled_unit(sDS, r, c * 4 + u, make_uint4(dd[4 * u], dd[4 * u + 1], dd[4 * u + 2], dd[4 * u + 3]));
         }
       }
       // shared-memory writes of these threads must be visible to the tensor core's reads
@@ -203,19 +207,20 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       // reading) as D/32 swizzled boxes of [128 rows x 32 floats], then add it into the global
       // accumulation buffer with tiled bulk reductions; rows past Sq are dropped by the hardware
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
+      for (int cc = 0; cc < D / 64; ++cc) {
+        const int c = half * (D / 64) + cc;
         uint32_t qr[32];
         tmem_ld32(tS + c * 32, qr);
         tmem_ld_wait(qr);
 #pragma unroll
         for (int u = 0; u < 8; ++u)
-          *reinterpret_cast<uint4*>(sP + c * kBoxBytes + tid * 128 + ((u ^ (tid & 7)) * 16)) =
+          *reinterpret_cast<uint4*>(sP + c * kBoxBytes + r * 128 + ((u ^ (r & 7)) * 16)) =
               make_uint4(qr[4 * u], qr[4 * u + 1], qr[4 * u + 2], qr[4 * u + 3]);
       }
       fence_proxy_async_smem();
       tcgen05_fence_before_sync();
       mbar_arrive(bar_s_free);
-      named_barrier_sync(1, 128);
+      named_barrier_sync(1, 256);
       if (tid == 0) {
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) tma_reduce_add_3d(&tm_dq, sP + c * kBoxBytes, c * 32, q0, bh);
@@ -224,16 +229,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
     if (tid == 0) tma_store_wait_all();  // the reductions must have landed before the CTA ends
 
-    // ---- epilogue: dK, dV of key row (k0 + tid) ----
-    const int kv_row = k0 + tid;
+    // ---- epilogue: key row (k0 + r); warps 0-3 write dK, warps 4-7 write dV ----
+    const int kv_row = k0 + r;
     const bool kv_ok = kv_row < prm.Sk;
     uint16_t* dk_row = static_cast<uint16_t*>(prm.dk) + b * prm.dk_stride_b + h * prm.dk_stride_h +
                        static_cast<int64_t>(kv_row) * prm.dk_stride_s;
     uint16_t* dv_row = static_cast<uint16_t*>(prm.dv) + b * prm.dv_stride_b + h * prm.dv_stride_h +
                        static_cast<int64_t>(kv_row) * prm.dv_stride_s;
     if (n_iter > 0) tcgen05_fence_after_sync();
-#pragma unroll
-    for (int which = 0; which < 2; ++which) {
+    {
+      const int which = half;
       const uint32_t tAcc = tmem_base + (which ? Cfg::kColDV : Cfg::kColDK) + lane_base;
       uint16_t* out_row = which ? dv_row : dk_row;
 #pragma unroll
@@ -259,7 +264,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
       }
     }
-  } else if (warp == 4) {
+  } else if (warp == 8) {
     // ================================ MMA issuer ================================
     constexpr uint32_t idesc_s = make_idesc(kBf16, kBlockM, kBlockN, 0, 0);  // S, dP: both K-major
     constexpr uint32_t idesc_t = make_idesc(kBf16, kBlockM, D, 1, 1);        // dV, dK: A M-major, B N-major
@@ -332,7 +337,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
   tcgen05_fence_before_sync();
   __syncthreads();
-  if (warp == 4) tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  if (warp == 8) tmem_dealloc(tmem_base, Cfg::kTmemCols);
 }
 
 }  // namespace fo
