@@ -165,6 +165,7 @@ extern "C" int fo_flash_attn_bwd(const void* q, const void* k, const void* v, co
   prm.scale = softmax_scale;
   prm.scale_log2 = softmax_scale * 1.4426950408889634f;
   prm.device_status = status;
+  prm.trace = fo::g_attn_trace;
   int rc;
   if (D == 128) rc = bf16 ? launch_bwd<128, true>(tq, tk, tv, tdo, tdq, prm, s) : launch_bwd<128, false>(tq, tk, tv, tdo, tdq, prm, s);
   else rc = bf16 ? launch_bwd<64, true>(tq, tk, tv, tdo, tdq, prm, s) : launch_bwd<64, false>(tq, tk, tv, tdo, tdq, prm, s);

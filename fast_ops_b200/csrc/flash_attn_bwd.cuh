@@ -41,7 +41,13 @@ struct AttnBwdParams {
   float scale;       // softmax scale
   float scale_log2;  // scale * log2(e)
   int* device_status;
+  unsigned long long* trace;  // optional timeline of CTA (0,0) (debug), or null
 };
+
+__device__ __forceinline__ void bwd_trace(const AttnBwdParams& prm, int role, int it, int ev) {
+  if (prm.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && (threadIdx.x & 31) == 0 && it < kTraceIters)
+    prm.trace[(role * kTraceIters + it) * kTraceEvents + ev] = clock64();
+}
 
 template <int D>
 struct BwdConfig {
@@ -160,12 +166,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const bool need_mask = (k0 + kBlockN > prm.Sk) || (prm.causal && k0 + kBlockN - 1 > q0);
       mbar_wait(bar_s_full, it & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_MMA);
       tcgen05_fence_after_sync();
-      // the P / dS buffers double as the staging area of the previous tile's dQ reduction: its
-      // shared-memory reads must have finished before they are overwritten
-      if (it > 0) {
-        if (tid == 0) tma_store_wait_read();
-        named_barrier_sync(1, 256);
-      }
+      if (warp == 0) bwd_trace(prm, 0, it, 0);
+      // P and dS of this thread's 64 columns, kept in registers (packed 16-bit) until the shared
+      // buffers are free
+      uint32_t pp[2][16], dd[2][16];
+      const float neg_delta_scale = -delta * prm.scale;
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
         const int c = half * 2 + cc;
@@ -174,35 +179,58 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         tmem_ld32(tDP + c * 32, dpr);
         tmem_ld_wait(sr);
         tmem_ld_wait(dpr);
-        uint32_t pp[16], dd[16];
+        // P in place over the S registers; the mask (rare: diagonal and ragged tiles) is a
+        // separate, warp-uniform branch so that full tiles pay nothing for it
 #pragma unroll
-        for (int x = 0; x < 32; x += 2) {
-          float p0 = fast_exp2(fmaf(__uint_as_float(sr[x]), prm.scale_log2, -lse2));
-          float p1 = fast_exp2(fmaf(__uint_as_float(sr[x + 1]), prm.scale_log2, -lse2));
-          if (need_mask) {
+        for (int x = 0; x < 32; ++x)
+          sr[x] = __float_as_uint(fast_exp2(fmaf(__uint_as_float(sr[x]), prm.scale_log2, -lse2)));
+        if (need_mask) {
+#pragma unroll
+          for (int x = 0; x < 32; ++x) {
             const int col = k0 + c * 32 + x;
-            if (col >= prm.Sk || (prm.causal && col > row)) p0 = 0.f;
-            if (col + 1 >= prm.Sk || (prm.causal && col + 1 > row)) p1 = 0.f;
+            if (col >= prm.Sk || (prm.causal && col > row)) sr[x] = 0u;
           }
-          const float d0 = p0 * (__uint_as_float(dpr[x]) - delta) * prm.scale;
-          const float d1 = p1 * (__uint_as_float(dpr[x + 1]) - delta) * prm.scale;
-          pp[x >> 1] = pack2<kBf16>(p0, p1);
-          dd[x >> 1] = pack2<kBf16>(d0, d1);
         }
 #pragma unroll
+        for (int x = 0; x < 32; x += 2) {
+          const float p0 = __uint_as_float(sr[x]), p1 = __uint_as_float(sr[x + 1]);
+          // dS = P * (dP - delta) * scale
+          const float d0 = p0 * fmaf(__uint_as_float(dpr[x]), prm.scale, neg_delta_scale);
+          const float d1 = p1 * fmaf(__uint_as_float(dpr[x + 1]), prm.scale, neg_delta_scale);
+          pp[cc][x >> 1] = pack2<kBf16>(p0, p1);
+          dd[cc][x >> 1] = pack2<kBf16>(d0, d1);
+        }
+      }
+      if (warp == 0) bwd_trace(prm, 0, it, 4);
+      // The P / dS buffers double as the staging area of the previous tile's dQ reduction, whose
+      // shared-memory reads take a few thousand cycles: they must have finished before the
+      // buffers are overwritten, which is why the arithmetic above runs first.
+      if (it > 0) {
+        if (tid == 0) tma_store_wait_read();
+        named_barrier_sync(1, 256);
+      }
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = half * 2 + cc;
+#pragma unroll
         for (int u = 0; u < 4; ++u) {
-          store_swizzled_unit(sP, r, c * 4 + u, make_uint4(pp[4 * u], pp[4 * u + 1], pp[4 * u + 2], pp[4 * u + 3]));
-          store_swizzled_unit(sDS, r, c * 4 + u, make_uint4(dd[4 * u], dd[4 * u + 1], dd[4 * u + 2], dd[4 * u + 3]));
+          store_swizzled_unit(sP, r, c * 4 + u,
+                              make_uint4(pp[cc][4 * u], pp[cc][4 * u + 1], pp[cc][4 * u + 2], pp[cc][4 * u + 3]));
+          store_swizzled_unit(sDS, r, c * 4 + u,
+                              make_uint4(dd[cc][4 * u], dd[cc][4 * u + 1], dd[cc][4 * u + 2], dd[cc][4 * u + 3]));
         }
       }
       // shared-memory writes of these threads must be visible to the tensor core's reads
       fence_proxy_async_smem();
+      if (warp == 0) bwd_trace(prm, 0, it, 5);
       tcgen05_fence_before_sync();
       mbar_arrive(bar_pds_full);
+      if (warp == 0) bwd_trace(prm, 0, it, 1);
 
       // dQ tile of this (query tile, key tile) pair -> fp32 accumulation buffer
       mbar_wait(bar_dq_full, it & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_MMA);
       tcgen05_fence_after_sync();
+      if (warp == 0) bwd_trace(prm, 0, it, 2);
       // stage the fp32 tile in shared memory (over P and dS, which the MMAs have finished
       // reading) as D/32 swizzled boxes of [128 rows x 32 floats], then add it into the global
       // accumulation buffer with tiled bulk reductions; rows past Sq are dropped by the hardware
@@ -220,6 +248,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       fence_proxy_async_smem();
       tcgen05_fence_before_sync();
       mbar_arrive(bar_s_free);
+      if (warp == 0) bwd_trace(prm, 0, it, 3);
       named_barrier_sync(1, 256);
       if (tid == 0) {
 #pragma unroll
@@ -282,6 +311,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     mbar_wait(bar_kv, 0, cta_abort, dstat, FO_STATUS_TIMEOUT_TMA);
     for (int it = 0; it < n_iter; ++it) {
       mbar_wait(bar_q_full, it & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_TMA);
+      bwd_trace(prm, 2, it, 0);
       if (it > 0) mbar_wait(bar_s_free, (it - 1) & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_SOFTMAX);
       tcgen05_fence_after_sync();
 #pragma unroll
@@ -295,9 +325,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         umma_ss_lo_elect(tDP, do_k + off, v_k + off, idesc_s, kk > 0 ? 1u : 0u);
       }
       tcgen05_commit_elect(bar_s_full);
+      bwd_trace(prm, 2, it, 1);
 
       mbar_wait(bar_pds_full, it & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_SOFTMAX);
       tcgen05_fence_after_sync();
+      bwd_trace(prm, 2, it, 2);
 #pragma unroll
       for (int kk = 0; kk < kBlockM / 16; ++kk)  // dV += P^T dO  (K = 16 query rows per step: 2048 bytes)
         umma_ss_lo_elect(tDV, p_m + kk * 128, do_n + kk * 128, idesc_t, (it > 0 || kk > 0) ? 1u : 0u);
@@ -312,6 +344,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         umma_ss_lo_elect(tS, ds_k + off, k_n + kk * 128, idesc_q, kk > 0 ? 1u : 0u);
       }
       tcgen05_commit_elect(bar_dq_full);
+      bwd_trace(prm, 2, it, 3);
     }
   } else {
     // ================================ TMA producer ================================

@@ -13,9 +13,15 @@
 #include "fo_host.h"
 #include "fo_tma.h"
 
+namespace fo {
+// Debug timeline buffer handed to the next attention launches (null = off).
+unsigned long long* g_attn_trace = nullptr;
+}  // namespace fo
+
 namespace {
 
 using fo::AttnParams;
+using fo::g_attn_trace;
 using fo::kBlockM;
 using fo::kBlockN;
 using fo::kBoxCols;
@@ -125,8 +131,6 @@ int set_smem(Kernel kernel, int bytes) {
   return FO_OK;
 }
 
-// Debug timeline buffer handed to the next attention launches (null = off).
-unsigned long long* g_attn_trace = nullptr;
 
 enum class AttnImpl { kSimple, kWarpSpecialized };
 

@@ -23,6 +23,9 @@ int* device_status_ptr(int device);  // device address of the word; nullptr on f
 
 extern std::atomic<int64_t> g_launch_count;
 
+// Device buffer for the attention kernels' debug timeline (fo_debug_set_attn_trace), or null.
+extern unsigned long long* g_attn_trace;
+
 // RAII: make `device` current for the scope, restore the previous one afterwards.
 struct DeviceGuard {
   int prev = -1;
