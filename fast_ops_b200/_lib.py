@@ -33,6 +33,18 @@ SIGNATURES = {
                                      _c.c_int, _c.c_int, _c.c_float, _c.c_int, _PTR]),
     "fo_flash_attn_bwd": (_c.c_int, [_PTR] * 11 + [_c.c_int] * 5 + [_I64P] * 8 +
                           [_c.c_int, _c.c_int, _c.c_float, _c.c_int, _PTR]),
+    "fo_flash_attn_fwd_ex": (_c.c_int, [_PTR, _PTR, _PTR, _PTR, _PTR,
+                                        _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
+                                        _I64P, _I64P, _I64P, _I64P,
+                                        _c.c_int, _c.c_int, _c.c_float,
+                                        _PTR, _I64P, _c.c_int, _c.c_float, _c.c_uint64, _c.c_uint64,
+                                        _c.c_int, _PTR]),
+    "fo_flash_attn_bwd_ex": (_c.c_int, [_PTR] * 11 + [_c.c_int] * 5 + [_I64P] * 8 +
+                             [_c.c_int, _c.c_int, _c.c_float,
+                              _PTR, _I64P, _c.c_int, _c.c_float, _c.c_uint64, _c.c_uint64,
+                              _c.c_int, _PTR]),
+    "fo_dropout_mask": (_c.c_int, [_PTR, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_float,
+                                   _c.c_uint64, _c.c_uint64, _c.c_int, _PTR]),
     "fo_lion_update": (_c.c_int, [_PTR, _PTR, _PTR, _c.c_int64, _c.c_int, _c.c_int, _c.c_int,
                                   _c.c_double, _c.c_double, _c.c_double, _c.c_double, _c.c_int, _PTR]),
     "fo_lion_multi_tensor_step": (_c.c_int, [_c.POINTER(_PTR), _c.POINTER(_PTR), _c.POINTER(_PTR), _I64P, _c.c_int,

@@ -3,6 +3,7 @@
 #include <cuda_fp16.h>
 
 #include <cmath>
+#include <cstring>
 
 #include "flash_attn_bwd.cuh"
 #include "fo_host.h"
@@ -64,10 +65,10 @@ attn_bwd_finish_dq_kernel(const float* __restrict__ dq_accum, uint16_t* __restri
   *reinterpret_cast<uint4*>(dq + b * q_sb + h * q_sh + row * q_ss + d0) = v;
 }
 
-template <int D, bool kBf16>
+template <int D, bool kBf16, bool kExt>
 int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
                const CUtensorMap& tdq, const fo::AttnBwdParams& prm, cudaStream_t stream) {
-  auto kernel = fo::attn_bwd_kernel<D, kBf16>;
+  auto kernel = fo::attn_bwd_kernel<D, kBf16, kExt>;
   constexpr int smem = fo::BwdConfig<D>::kSmemBytes;
   FO_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   dim3 grid((prm.Sk + fo::kBlockN - 1) / fo::kBlockN, prm.B * prm.H);
@@ -85,15 +86,20 @@ int check_out_strides(const int64_t s[3], const char* name) {
 
 }  // namespace
 
-extern "C" int fo_flash_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout,
-                                 const float* lse, void* dq, void* dk, void* dv, float* dq_accum, float* delta,
-                                 int B, int H, int Sq, int Sk, int D,
-                                 const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
-                                 const int64_t o_strides[3], const int64_t do_strides[3],
-                                 const int64_t dq_strides[3], const int64_t dk_strides[3],
-                                 const int64_t dv_strides[3],
-                                 int dtype, int causal, float softmax_scale, int device, void* stream) {
-  fo::clear_error();
+namespace fo {
+int make_attn_extras(AttnExtras* ex, const void* bias, const int64_t* bias_strides, int bias_dtype, int dtype,
+                     float dropout_p, uint64_t rng_seed, uint64_t rng_offset);  // flash_attn_fwd.cu
+}
+
+static int attn_bwd_impl(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                         const float* lse, void* dq, void* dk, void* dv, float* dq_accum, float* delta,
+                         int B, int H, int Sq, int Sk, int D,
+                         const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
+                         const int64_t o_strides[3], const int64_t do_strides[3],
+                         const int64_t dq_strides[3], const int64_t dk_strides[3],
+                         const int64_t dv_strides[3],
+                         int dtype, int causal, float softmax_scale, const fo::AttnExtras* ex, int device,
+                         void* stream) {
   FO_REQUIRE(q && k && v && o && dout && lse && dq && dk && dv && dq_accum && delta, "null pointer");
   FO_REQUIRE(q_strides && k_strides && v_strides && o_strides && do_strides && dq_strides && dk_strides && dv_strides,
              "null stride array");
@@ -166,9 +172,18 @@ extern "C" int fo_flash_attn_bwd(const void* q, const void* k, const void* v, co
   prm.scale_log2 = softmax_scale * 1.4426950408889634f;
   prm.device_status = status;
   prm.trace = fo::g_attn_trace;
+  std::memset(&prm.ex, 0, sizeof(prm.ex));
+  prm.ex.drop_rescale = 1.f;
+  const bool ext = ex != nullptr && (ex->bias != nullptr || ex->dropout);
+  if (ext) prm.ex = *ex;
   int rc;
-  if (D == 128) rc = bf16 ? launch_bwd<128, true>(tq, tk, tv, tdo, tdq, prm, s) : launch_bwd<128, false>(tq, tk, tv, tdo, tdq, prm, s);
-  else rc = bf16 ? launch_bwd<64, true>(tq, tk, tv, tdo, tdq, prm, s) : launch_bwd<64, false>(tq, tk, tv, tdo, tdq, prm, s);
+  if (ext) {
+    if (D == 128) rc = bf16 ? launch_bwd<128, true, true>(tq, tk, tv, tdo, tdq, prm, s) : launch_bwd<128, false, true>(tq, tk, tv, tdo, tdq, prm, s);
+    else rc = bf16 ? launch_bwd<64, true, true>(tq, tk, tv, tdo, tdq, prm, s) : launch_bwd<64, false, true>(tq, tk, tv, tdo, tdq, prm, s);
+  } else {
+    if (D == 128) rc = bf16 ? launch_bwd<128, true, false>(tq, tk, tv, tdo, tdq, prm, s) : launch_bwd<128, false, false>(tq, tk, tv, tdo, tdq, prm, s);
+    else rc = bf16 ? launch_bwd<64, true, false>(tq, tk, tv, tdo, tdq, prm, s) : launch_bwd<64, false, false>(tq, tk, tv, tdo, tdq, prm, s);
+  }
   if (rc) return rc;
 
   {
@@ -185,4 +200,39 @@ extern "C" int fo_flash_attn_bwd(const void* q, const void* k, const void* v, co
     FO_CUDA_CHECK(cudaGetLastError());
   }
   return FO_OK;
+}
+
+extern "C" int fo_flash_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                                 const float* lse, void* dq, void* dk, void* dv, float* dq_accum, float* delta,
+                                 int B, int H, int Sq, int Sk, int D,
+                                 const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
+                                 const int64_t o_strides[3], const int64_t do_strides[3],
+                                 const int64_t dq_strides[3], const int64_t dk_strides[3],
+                                 const int64_t dv_strides[3],
+                                 int dtype, int causal, float softmax_scale, int device, void* stream) {
+  fo::clear_error();
+  return attn_bwd_impl(q, k, v, o, dout, lse, dq, dk, dv, dq_accum, delta, B, H, Sq, Sk, D, q_strides, k_strides,
+                       v_strides, o_strides, do_strides, dq_strides, dk_strides, dv_strides, dtype, causal,
+                       softmax_scale, nullptr, device, stream);
+}
+
+extern "C" int fo_flash_attn_bwd_ex(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                                    const float* lse, void* dq, void* dk, void* dv, float* dq_accum, float* delta,
+                                    int B, int H, int Sq, int Sk, int D,
+                                    const int64_t q_strides[3], const int64_t k_strides[3],
+                                    const int64_t v_strides[3], const int64_t o_strides[3],
+                                    const int64_t do_strides[3], const int64_t dq_strides[3],
+                                    const int64_t dk_strides[3], const int64_t dv_strides[3],
+                                    int dtype, int causal, float softmax_scale,
+                                    const void* bias, const int64_t bias_strides[3], int bias_dtype,
+                                    float dropout_p, uint64_t rng_seed, uint64_t rng_offset,
+                                    int device, void* stream) {
+  fo::clear_error();
+  FO_REQUIRE(dtype == FO_F16 || dtype == FO_BF16, "attention tensors must be fp16 or bf16 (got dtype %d)", dtype);
+  fo::AttnExtras ex;
+  if (int rc = fo::make_attn_extras(&ex, bias, bias_strides, bias_dtype, dtype, dropout_p, rng_seed, rng_offset))
+    return rc;
+  return attn_bwd_impl(q, k, v, o, dout, lse, dq, dk, dv, dq_accum, delta, B, H, Sq, Sk, D, q_strides, k_strides,
+                       v_strides, o_strides, do_strides, dq_strides, dk_strides, dv_strides, dtype, causal,
+                       softmax_scale, &ex, device, stream);
 }

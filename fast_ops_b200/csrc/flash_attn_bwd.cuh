@@ -19,8 +19,9 @@
 //
 // Warps 0-7: two threads per query row, each taking half of the tile's columns (no reduction
 // across a row is needed in the backward), and in the epilogue one thread per key row for dK
-// (warps 0-3) and dV (warps 4-7); warp 8 issues the MMAs; warp 9 issues the TMA loads.  This first version runs the steps of a query tile in order, with
-// no overlap between tiles.
+// (warps 0-3) and dV (warps 4-7); warp 8 issues the MMAs; warp 9 issues the TMA loads.  The steps
+// of a query tile run in order; the load of the next Q / dO tile and the drain of the previous
+// dQ reduction overlap them.
 #pragma once
 
 #include "flash_attn_common.cuh"
@@ -42,6 +43,7 @@ struct AttnBwdParams {
   float scale_log2;  // scale * log2(e)
   int* device_status;
   unsigned long long* trace;  // optional timeline of CTA (0,0) (debug), or null
+  AttnExtras ex;  // bias / dropout of the forward; read only by the kernel variants built for them
 };
 
 __device__ __forceinline__ void bwd_trace(const AttnBwdParams& prm, int role, int it, int ev) {
@@ -76,7 +78,7 @@ __device__ __forceinline__ void store_swizzled_unit(uint8_t* tile, int r, int u,
 }
 
 // grid = (key tiles, B*H); block = 320.
-template <int D, bool kBf16>
+template <int D, bool kBf16, bool kExt>
 __global__ void __launch_bounds__(320, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
@@ -155,13 +157,29 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tS = tmem_base + Cfg::kColS + lane_base;
     const uint32_t tDP = tmem_base + Cfg::kColDP + lane_base;
+    const bool has_bias = kExt && prm.ex.bias != nullptr;
+    const bool has_drop = kExt && prm.ex.dropout;
+    // with dropout dP arrives without the 1 / (1 - p) factor of the kept elements
+    const float dp_scale = kExt ? prm.scale * prm.ex.drop_rescale : prm.scale;
     for (int it = 0; it < n_iter; ++it) {
       const int i = i0 + it;
       const int q0 = i * kBlockM;
       const int row = q0 + r;
       const bool row_ok = row < prm.Sq;
-      // a row past the end gets LSE = +inf, so its P and dS are exactly 0
-      const float lse2 = row_ok ? prm.lse[static_cast<int64_t>(bh) * prm.Sq + row] * 1.4426950408889634f : INFINITY;
+      // a row past the end, or one whose keys are all masked (LSE = -inf), gets LSE = +inf, so
+      // that its P and dS are exactly 0
+      const float lse_nat = row_ok ? prm.lse[static_cast<int64_t>(bh) * prm.Sq + row] : INFINITY;
+      const float lse2 = (lse_nat == -INFINITY) ? INFINITY : lse_nat * 1.4426950408889634f;
+      const uint8_t* bias_row = nullptr;
+      uint32_t drop_row = 0;
+      if constexpr (kExt) {
+        if (has_bias && row_ok)
+          bias_row = static_cast<const uint8_t*>(prm.ex.bias) +
+                     (b * prm.ex.bias_stride_b + h * prm.ex.bias_stride_h + static_cast<int64_t>(row) * prm.ex.bias_stride_q) *
+                         (prm.ex.bias_f32 ? 4 : 2);
+        drop_row = prm.ex.drop_base + static_cast<uint32_t>(bh) * static_cast<uint32_t>(prm.Sq) * static_cast<uint32_t>(prm.Sk) +
+                   static_cast<uint32_t>(row) * static_cast<uint32_t>(prm.Sk);
+      }
       const float delta = row_ok ? prm.delta[static_cast<int64_t>(bh) * prm.Sq + row] : 0.f;
       const bool need_mask = (k0 + kBlockN > prm.Sk) || (prm.causal && k0 + kBlockN - 1 > q0);
       mbar_wait(bar_s_full, it & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_MMA);
@@ -177,13 +195,25 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         uint32_t sr[32], dpr[32];
         tmem_ld32(tS + c * 32, sr);
         tmem_ld32(tDP + c * 32, dpr);
+        float bb[kExt ? 32 : 1];
+        if constexpr (kExt) {
+          if (has_bias) load_bias32<kBf16>(prm.ex, bias_row, k0 + c * 32, prm.Sk, bb);
+        }
         tmem_ld_wait(sr);
         tmem_ld_wait(dpr);
         // P in place over the S registers; the mask (rare: diagonal and ragged tiles) is a
         // separate, warp-uniform branch so that full tiles pay nothing for it
+        if (has_bias) {
+          if constexpr (kExt) {
 #pragma unroll
-        for (int x = 0; x < 32; ++x)
-          sr[x] = __float_as_uint(fast_exp2(fmaf(__uint_as_float(sr[x]), prm.scale_log2, -lse2)));
+            for (int x = 0; x < 32; ++x)
+              sr[x] = __float_as_uint(fast_exp2(fmaf(__uint_as_float(sr[x]), prm.scale_log2, bb[x]) - lse2));
+          }
+        } else {
+#pragma unroll
+          for (int x = 0; x < 32; ++x)
+            sr[x] = __float_as_uint(fast_exp2(fmaf(__uint_as_float(sr[x]), prm.scale_log2, -lse2)));
+        }
         if (need_mask) {
 #pragma unroll
           for (int x = 0; x < 32; ++x) {
@@ -194,10 +224,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
         for (int x = 0; x < 32; x += 2) {
           const float p0 = __uint_as_float(sr[x]), p1 = __uint_as_float(sr[x + 1]);
-          // dS = P * (dP - delta) * scale
-          const float d0 = p0 * fmaf(__uint_as_float(dpr[x]), prm.scale, neg_delta_scale);
-          const float d1 = p1 * fmaf(__uint_as_float(dpr[x + 1]), prm.scale, neg_delta_scale);
-          pp[cc][x >> 1] = pack2<kBf16>(p0, p1);
+          float z0 = p0, z1 = p1;  // P as it enters dV: zero where the forward dropped the element
+          float g0 = __uint_as_float(dpr[x]), g1 = __uint_as_float(dpr[x + 1]);
+          if constexpr (kExt) {
+            if (has_drop) {
+              const uint32_t idx = drop_row + static_cast<uint32_t>(k0 + c * 32 + x);
+              if (dropout_hash(idx, prm.ex.drop_seed) <= prm.ex.drop_threshold) { z0 = 0.f; g0 = 0.f; }
+              if (dropout_hash(idx + 1u, prm.ex.drop_seed) <= prm.ex.drop_threshold) { z1 = 0.f; g1 = 0.f; }
+            }
+          }
+          // dS = P * (dP - delta) * scale, dP = 0 for a dropped element
+          const float d0 = p0 * fmaf(g0, dp_scale, neg_delta_scale);
+          const float d1 = p1 * fmaf(g1, dp_scale, neg_delta_scale);
+          pp[cc][x >> 1] = pack2<kBf16>(z0, z1);
           dd[cc][x >> 1] = pack2<kBf16>(d0, d1);
         }
       }
@@ -270,6 +309,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const int which = half;
       const uint32_t tAcc = tmem_base + (which ? Cfg::kColDV : Cfg::kColDK) + lane_base;
       uint16_t* out_row = which ? dv_row : dk_row;
+      // dV was accumulated from the kept P without the dropout factor
+      const float out_scale = (kExt && which) ? prm.ex.drop_rescale : 1.f;
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
         uint32_t ar[32];
@@ -284,6 +325,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
           for (int x = 0; x < 32; x += 8) {
             uint4 v;
+            if constexpr (kExt) {
+#pragma unroll
+              for (int y = 0; y < 8; ++y) ar[x + y] = __float_as_uint(__uint_as_float(ar[x + y]) * out_scale);
+            }
             v.x = pack2<kBf16>(__uint_as_float(ar[x + 0]), __uint_as_float(ar[x + 1]));
             v.y = pack2<kBf16>(__uint_as_float(ar[x + 2]), __uint_as_float(ar[x + 3]));
             v.z = pack2<kBf16>(__uint_as_float(ar[x + 4]), __uint_as_float(ar[x + 5]));

@@ -14,6 +14,77 @@ constexpr int kBlockN = 128;  // key/value rows per tile
 constexpr int kBoxCols = 64;  // elements per TMA box row: 128 bytes, one swizzle span
 constexpr int kBoxBytes = kBlockN * kBoxCols * 2;  // 16 KiB: a [128 x 64] 16-bit box
 
+// Optional additive bias and dropout of the extended entry points (all zero: plain attention).
+struct AttnExtras {
+  const void* bias;  // null: none; element (b, h, i, j) at bias + b*stride_b + h*stride_h + i*stride_q + j
+  int64_t bias_stride_b, bias_stride_h, bias_stride_q;  // elements; 0 along a broadcast dimension
+  int bias_f32;   // 1: fp32 bias, 0: the 16-bit type of Q
+  int bias_vec;   // 1: every bias row starts on a 16-byte boundary (vector loads allowed)
+  int dropout;    // 1: dropout on
+  uint32_t drop_threshold;  // an element is kept iff dropout_hash(index, seed) > threshold
+  uint32_t drop_seed;
+  uint32_t drop_base;       // low 32 bits of the generator offset
+  float drop_rescale;       // 1 / (1 - p), or 1 when dropout is off
+};
+
+// Keep/drop decision of element `idx` (fast_ops/flash_attention/flash_attention_triton.py:38-50:
+// an integer hash in place of a Philox draw; all arithmetic modulo 2^32).
+__device__ __forceinline__ uint32_t dropout_hash(uint32_t idx, uint32_t seed) {
+  uint32_t a = idx ^ seed;
+  a ^= a >> 4;
+  a = (a ^ 0xDEADBEEFu) + (a << 5);
+  a ^= a >> 11;
+  return a;
+}
+
+// out[i] = log2(e) * bias[col0 + i] for the 32 columns col0.. of one bias row (`rowp` points at
+// column 0 of the row, or is null for a row past the end); columns >= Sk give 0.
+template <bool kBf16>
+__device__ __forceinline__ void load_bias32(const AttnExtras& ex, const uint8_t* rowp, int col0, int Sk,
+                                            float (&out)[32]) {
+  constexpr float kLog2e = 1.4426950408889634f;
+  if (rowp == nullptr) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) out[i] = 0.f;
+    return;
+  }
+  const bool full = ex.bias_vec && (col0 + 32 <= Sk);
+  if (ex.bias_f32) {
+    const float* p = reinterpret_cast<const float*>(rowp) + col0;
+    if (full) {
+#pragma unroll
+      for (int i = 0; i < 32; i += 4) {
+        const float4 v = __ldg(reinterpret_cast<const float4*>(p + i));
+        out[i] = v.x * kLog2e; out[i + 1] = v.y * kLog2e; out[i + 2] = v.z * kLog2e; out[i + 3] = v.w * kLog2e;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) out[i] = (col0 + i < Sk) ? __ldg(p + i) * kLog2e : 0.f;
+    }
+  } else {
+    const uint16_t* p = reinterpret_cast<const uint16_t*>(rowp) + col0;
+    auto cvt = [](uint16_t h) -> float {
+      if constexpr (kBf16) return __uint_as_float(static_cast<uint32_t>(h) << 16);
+      else return __half2float(__ushort_as_half(h));
+    };
+    if (full) {
+#pragma unroll
+      for (int i = 0; i < 32; i += 8) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(p + i));
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          out[i + 2 * t] = cvt(static_cast<uint16_t>(w[t] & 0xffffu)) * kLog2e;
+          out[i + 2 * t + 1] = cvt(static_cast<uint16_t>(w[t] >> 16)) * kLog2e;
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) out[i] = (col0 + i < Sk) ? cvt(__ldg(p + i)) * kLog2e : 0.f;
+    }
+  }
+}
+
 struct AttnParams {
   void* o;
   float* lse;  // may be null
@@ -27,6 +98,7 @@ struct AttnParams {
   int kv_head_bcast;  // 1: K and V have one head shared by all query heads (multi-query attention)
   // Optional timeline of CTA 0 (debug): [role][key tile][event] SM clock values, or null.
   unsigned long long* trace;
+  AttnExtras ex;  // read only by the kernel variants built for bias / dropout
 };
 
 constexpr int kTraceRoles = 3;   // softmax tile 0, softmax tile 1, MMA issuer

@@ -3,6 +3,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
@@ -156,12 +157,49 @@ int launch_simple(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMa
 
 }  // namespace
 
-extern "C" int fo_flash_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
-                                 int B, int H, int Sq, int Sk, int D,
-                                 const int64_t q_strides[3], const int64_t k_strides[3],
-                                 const int64_t v_strides[3], const int64_t o_strides[3],
-                                 int dtype, int causal, float softmax_scale, int device, void* stream) {
-  fo::clear_error();
+namespace fo {
+
+// Validates the optional bias / dropout arguments of the extended entry points and fills `ex`.
+int make_attn_extras(AttnExtras* ex, const void* bias, const int64_t* bias_strides, int bias_dtype, int dtype,
+                     float dropout_p, uint64_t rng_seed, uint64_t rng_offset) {
+  std::memset(ex, 0, sizeof(*ex));
+  ex->drop_rescale = 1.f;
+  if (bias != nullptr) {
+    FO_REQUIRE(bias_strides != nullptr, "bias given without strides");
+    FO_REQUIRE(bias_dtype == FO_F32 || bias_dtype == dtype,
+               "bias must be fp32 or have the dtype of q (got dtype %d)", bias_dtype);
+    for (int i = 0; i < 3; ++i) FO_REQUIRE(bias_strides[i] >= 0, "bias: strides must be non-negative");
+    ex->bias = bias;
+    ex->bias_stride_b = bias_strides[0];
+    ex->bias_stride_h = bias_strides[1];
+    ex->bias_stride_q = bias_strides[2];
+    ex->bias_f32 = bias_dtype == FO_F32;
+    const int per16 = ex->bias_f32 ? 4 : 8;  // elements per 16 bytes
+    ex->bias_vec = (reinterpret_cast<uintptr_t>(bias) & 15) == 0 && bias_strides[0] % per16 == 0 &&
+                   bias_strides[1] % per16 == 0 && bias_strides[2] % per16 == 0;
+  }
+  FO_REQUIRE(dropout_p >= 0.f && dropout_p < 1.f, "dropout_p must be in [0, 1) (got %g)", (double)dropout_p);
+  if (dropout_p > 0.f) {
+    ex->dropout = 1;
+    // fast_ops/flash_attention/flash_attention_triton.py:50: keep iff hash > uint32(p * 4294967295),
+    // the product formed in fp32 (where 4294967295 rounds to 2^32) and truncated
+    const float prod = dropout_p * 4294967296.f;
+    ex->drop_threshold = prod >= 4294967296.f ? 0xffffffffu : static_cast<uint32_t>(prod);
+    ex->drop_seed = static_cast<uint32_t>(rng_seed);
+    ex->drop_base = static_cast<uint32_t>(rng_offset);
+    ex->drop_rescale = 1.f / (1.f - dropout_p);
+  }
+  return FO_OK;
+}
+
+}  // namespace fo
+
+static int attn_fwd_impl(const void* q, const void* k, const void* v, void* o, float* lse,
+                         int B, int H, int Sq, int Sk, int D,
+                         const int64_t q_strides[3], const int64_t k_strides[3],
+                         const int64_t v_strides[3], const int64_t o_strides[3],
+                         int dtype, int causal, float softmax_scale, const fo::AttnExtras* ex,
+                         int device, void* stream) {
   FO_REQUIRE(q && k && v && o, "null tensor pointer");
   FO_REQUIRE(q_strides && k_strides && v_strides && o_strides, "null stride array");
   FO_REQUIRE(dtype == FO_F16 || dtype == FO_BF16, "attention inputs must be fp16 or bf16 (got dtype %d)", dtype);
@@ -210,6 +248,10 @@ extern "C" int fo_flash_attn_fwd(const void* q, const void* k, const void* v, vo
   prm.num_q_tiles = (Sq + kBlockM - 1) / kBlockM;
   prm.trace = g_attn_trace;
   prm.kv_head_bcast = kv_bcast ? 1 : 0;
+  std::memset(&prm.ex, 0, sizeof(prm.ex));
+  prm.ex.drop_rescale = 1.f;
+  const bool ext = ex != nullptr && (ex->bias != nullptr || ex->dropout);
+  if (ext) prm.ex = *ex;
   {
     // as many heads per group as keep their K and V (2 * Sk * D * 2 bytes each) within about a
     // third of the 126 MB L2, leaving room for Q, O and the other traffic
@@ -224,12 +266,71 @@ extern "C" int fo_flash_attn_fwd(const void* q, const void* k, const void* v, vo
 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool bf16 = dtype == FO_BF16;
+  if (ext) {  // bias and dropout exist in the warp-specialised kernel only
+    if (D == 128) return bf16 ? fo::launch_ws<128, true, true>(tq, tk, tv, prm, s) : fo::launch_ws<128, false, true>(tq, tk, tv, prm, s);
+    return bf16 ? fo::launch_ws<64, true, true>(tq, tk, tv, prm, s) : fo::launch_ws<64, false, true>(tq, tk, tv, prm, s);
+  }
   if (chosen_impl() == AttnImpl::kWarpSpecialized) {
-    if (D == 128) return bf16 ? fo::launch_ws<128, true>(tq, tk, tv, prm, s) : fo::launch_ws<128, false>(tq, tk, tv, prm, s);
-    return bf16 ? fo::launch_ws<64, true>(tq, tk, tv, prm, s) : fo::launch_ws<64, false>(tq, tk, tv, prm, s);
+    if (D == 128) return bf16 ? fo::launch_ws<128, true, false>(tq, tk, tv, prm, s) : fo::launch_ws<128, false, false>(tq, tk, tv, prm, s);
+    return bf16 ? fo::launch_ws<64, true, false>(tq, tk, tv, prm, s) : fo::launch_ws<64, false, false>(tq, tk, tv, prm, s);
   }
   if (D == 128) return bf16 ? launch_simple<128, true>(tq, tk, tv, prm, s) : launch_simple<128, false>(tq, tk, tv, prm, s);
   return bf16 ? launch_simple<64, true>(tq, tk, tv, prm, s) : launch_simple<64, false>(tq, tk, tv, prm, s);
+}
+
+extern "C" int fo_flash_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
+                                 int B, int H, int Sq, int Sk, int D,
+                                 const int64_t q_strides[3], const int64_t k_strides[3],
+                                 const int64_t v_strides[3], const int64_t o_strides[3],
+                                 int dtype, int causal, float softmax_scale, int device, void* stream) {
+  fo::clear_error();
+  return attn_fwd_impl(q, k, v, o, lse, B, H, Sq, Sk, D, q_strides, k_strides, v_strides, o_strides, dtype, causal,
+                       softmax_scale, nullptr, device, stream);
+}
+
+extern "C" int fo_flash_attn_fwd_ex(const void* q, const void* k, const void* v, void* o, float* lse,
+                                    int B, int H, int Sq, int Sk, int D,
+                                    const int64_t q_strides[3], const int64_t k_strides[3],
+                                    const int64_t v_strides[3], const int64_t o_strides[3],
+                                    int dtype, int causal, float softmax_scale,
+                                    const void* bias, const int64_t bias_strides[3], int bias_dtype,
+                                    float dropout_p, uint64_t rng_seed, uint64_t rng_offset,
+                                    int device, void* stream) {
+  fo::clear_error();
+  FO_REQUIRE(dtype == FO_F16 || dtype == FO_BF16, "attention inputs must be fp16 or bf16 (got dtype %d)", dtype);
+  fo::AttnExtras ex;
+  if (int rc = fo::make_attn_extras(&ex, bias, bias_strides, bias_dtype, dtype, dropout_p, rng_seed, rng_offset))
+    return rc;
+  return attn_fwd_impl(q, k, v, o, lse, B, H, Sq, Sk, D, q_strides, k_strides, v_strides, o_strides, dtype, causal,
+                       softmax_scale, &ex, device, stream);
+}
+
+// out[b, h, i, j] = 1 if element (i, j) of head (b, h) is kept by the dropout of
+// fo_flash_attn_fwd_ex called with the same p, seed and offset; dense (B, H, Sq, Sk) bytes.
+__global__ void dropout_mask_kernel(uint8_t* __restrict__ out, int64_t total, uint32_t base, uint32_t seed,
+                                    uint32_t threshold) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride)
+    out[i] = fo::dropout_hash(base + static_cast<uint32_t>(i), seed) > threshold ? 1 : 0;
+}
+
+extern "C" int fo_dropout_mask(uint8_t* out, int B, int H, int Sq, int Sk, float dropout_p, uint64_t rng_seed,
+                               uint64_t rng_offset, int device, void* stream) {
+  fo::clear_error();
+  FO_REQUIRE(out != nullptr, "null output pointer");
+  FO_REQUIRE(B > 0 && H > 0 && Sq > 0 && Sk > 0, "B, H, Sq, Sk must be positive");
+  FO_REQUIRE(dropout_p > 0.f && dropout_p < 1.f, "dropout_p must be in (0, 1) (got %g)", (double)dropout_p);
+  fo::AttnExtras ex;
+  if (int rc = fo::make_attn_extras(&ex, nullptr, nullptr, FO_F32, FO_BF16, dropout_p, rng_seed, rng_offset)) return rc;
+  fo::DeviceGuard guard(device);
+  FO_REQUIRE(guard.ok, "cannot make device %d current", device);
+  const int64_t total = static_cast<int64_t>(B) * H * Sq * Sk;
+  const int blocks = static_cast<int>(std::min<int64_t>((total + 255) / 256, 148 * 16));
+  dropout_mask_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(out, total, ex.drop_base, ex.drop_seed,
+                                                                            ex.drop_threshold);
+  fo::g_launch_count.fetch_add(1, std::memory_order_relaxed);
+  FO_CUDA_CHECK(cudaGetLastError());
+  return FO_OK;
 }
 
 extern "C" int fo_debug_umma_tile(const void* a, const void* b, float* c, int N, int K, int dtype, int mode,

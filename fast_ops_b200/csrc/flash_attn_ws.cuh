@@ -62,7 +62,9 @@ template <int kRegs> __device__ __forceinline__ void reg_dealloc() {
 // grid = (num_q_pairs * B * H); block = 512.  Consecutive blocks sweep a group of heads whose K
 // and V fit in L2 together, so the query tiles of those heads re-read K/V from L2 rather than
 // from HBM; within the group the pairs with the most key tiles (causal mask) start first.
-template <int D, bool kBf16>
+// kExt builds the variant with the optional additive bias and dropout (prm.ex); the plain
+// variant contains none of that code.
+template <int D, bool kBf16, bool kExt>
 __global__ void __launch_bounds__(512, 1)
 attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                    const __grid_constant__ CUtensorMap tm_v, const AttnParams prm) {
@@ -161,6 +163,21 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     const uint32_t tS = tmem_base + Cfg::kColS0 + s * kBlockN + lane_base;
     float* alpha_slot = s_alpha + s * 256 + r;
     float m_run = -INFINITY, l_run = 0.f;
+    // bias row of this thread (null: no bias, or a row past the end) and the dropout index of
+    // its column 0; with a bias the scores are scaled when the bias is added, not in the exponent
+    const bool has_bias = kExt && prm.ex.bias != nullptr;
+    const bool has_drop = kExt && prm.ex.dropout;
+    const uint8_t* bias_row = nullptr;
+    uint32_t drop_row = 0;
+    if constexpr (kExt) {
+      if (has_bias && row < prm.Sq)
+        bias_row = static_cast<const uint8_t*>(prm.ex.bias) +
+                   (b * prm.ex.bias_stride_b + h * prm.ex.bias_stride_h + static_cast<int64_t>(row) * prm.ex.bias_stride_q) *
+                       (prm.ex.bias_f32 ? 4 : 2);
+      drop_row = prm.ex.drop_base + static_cast<uint32_t>(bh) * static_cast<uint32_t>(prm.Sq) * static_cast<uint32_t>(prm.Sk) +
+                 static_cast<uint32_t>(row) * static_cast<uint32_t>(prm.Sk);
+    }
+    const float exp_scale = has_bias ? 1.f : prm.scale_log2;
 
     for (int j = 0; j < n_s; ++j) {
       const int k0 = j * kBlockN;
@@ -187,6 +204,15 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 #if FO_WS_PIPE_LD == 1
         if (c + 1 < 4) tmem_ld32(tS + (c + 1) * 32, sr[c + 1]);
 #endif
+        if constexpr (kExt) {
+          if (has_bias) {
+            float bb[32];
+            load_bias32<kBf16>(prm.ex, bias_row, k0 + c * 32, prm.Sk, bb);
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              sr[c][i] = __float_as_uint(fmaf(__uint_as_float(sr[c][i]), prm.scale_log2, bb[i]));
+          }
+        }
         if (need_mask) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
@@ -208,13 +234,13 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       }
       const float mx = fmaxf(fmaxf(mxa, mxb), fmaxf(mxc, mxd));
       if ((warp & 3) == 0) trace_event(prm, s, j, 5);
-      const float m_cand = fmaxf(m_run, mx * prm.scale_log2);
+      const float m_cand = fmaxf(m_run, mx * exp_scale);
       const float m_new = (m_cand - m_run > kRescaleThreshold) ? m_cand : m_run;
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
       const float alpha = (m_new == m_run) ? 1.f : fast_exp2(m_run - m_use);
       // P = exp2(S * scale - m): packed fp32 pairs for the multiply-add and the row sum, one
       // unrolled block over the whole tile so that ex2 latencies overlap across chunks.
-      const float2 sc2 = make_float2(prm.scale_log2, prm.scale_log2);
+      const float2 sc2 = make_float2(exp_scale, exp_scale);
       const float2 nm2 = make_float2(-m_use, -m_use);
       float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
       uint32_t pr[4][16];
@@ -226,6 +252,15 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           x.x = fast_exp2(x.x);
           x.y = fast_exp2(x.y);
           if (q & 1) acc1 = __fadd2_rn(acc1, x); else acc0 = __fadd2_rn(acc0, x);
+          if constexpr (kExt) {
+            // dropped elements leave the row sum untouched and enter P V as zeros; the factor
+            // 1 / (1 - p) is applied once, to O, in the epilogue
+            if (has_drop) {
+              const uint32_t idx = drop_row + static_cast<uint32_t>(k0 + c * 32 + 2 * q);
+              if (dropout_hash(idx, prm.ex.drop_seed) <= prm.ex.drop_threshold) x.x = 0.f;
+              if (dropout_hash(idx + 1u, prm.ex.drop_seed) <= prm.ex.drop_threshold) x.y = 0.f;
+            }
+          }
           pr[c][q] = pack2<kBf16>(x.x, x.y);
         }
         if (c == 0) {
@@ -292,7 +327,8 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       tcgen05_fence_after_sync();
       const float l_run = s_final[s * 256 + r];
       const float m_run = s_final[s * 256 + 128 + r];
-      const float inv_l = (l_run > 0.f) ? 1.f / l_run : 0.f;
+      const float o_scale = kExt ? prm.ex.drop_rescale : 1.f;
+      const float inv_l = (l_run > 0.f) ? o_scale / l_run : 0.f;
       const int row = (2 * pair + s) * kBlockM + r;
       const bool row_ok = row < prm.Sq;
       uint16_t* orow = static_cast<uint16_t*>(prm.o) + b * prm.o_stride_b + h * prm.o_stride_h +
@@ -434,10 +470,10 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   if (warp == 12) tmem_dealloc(tmem_base, Cfg::kTmemCols);
 }
 
-template <int D, bool kBf16>
+template <int D, bool kBf16, bool kExt>
 int launch_ws(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& prm,
               cudaStream_t stream) {
-  auto kernel = attn_fwd_ws_kernel<D, kBf16>;
+  auto kernel = attn_fwd_ws_kernel<D, kBf16, kExt>;
   constexpr int smem = WsConfig<D>::kSmemBytes;
   // The attribute is per device; setting it again is cheap and keeps multi-device callers right.
   cudaError_t ea = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);

@@ -25,11 +25,72 @@ def _strides3(t: Tensor):
     return (ctypes.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
 
 
+def _prepare_bias(bias: Optional[Tensor], Q: Tensor, N: int):
+    """Checks a bias the way the reference does (flash_attention_triton.py:752-769) and returns
+    (tensor kept alive, pointer, stride array, dtype code) for the C ABI."""
+    if bias is None:
+        return None, None, None, _lib.FO_F32
+    B, H, M, _ = Q.shape
+    if bias.dtype not in (Q.dtype, torch.float32):
+        raise RuntimeError(f"bias must be float32 or have Q's dtype, got {bias.dtype}")
+    if not bias.is_cuda or bias.device != Q.device:
+        raise RuntimeError("bias must be on Q's device")
+    if bias.dim() != 4:
+        raise RuntimeError("bias must be 4-D, broadcastable to (B, H, M, N)")
+    if bias.stride(-1) != 1:
+        bias = bias.contiguous()
+    if tuple(bias.shape[2:]) not in ((1, N), (M, N)):
+        raise RuntimeError("Last 2 dimensions of bias must be (1, seqlen_k) or (seqlen_q, seqlen_k)")
+    if bias.shape[0] not in (1, B) or bias.shape[1] not in (1, H):
+        raise RuntimeError("bias batch and head dimensions must be 1 or match Q")
+    bias = bias.expand(B, H, M, N)
+    return bias, bias.data_ptr(), _strides3(bias), _lib.dtype_code(bias.dtype)
+
+
+def next_dropout_rng(device: torch.device, count: int) -> Tuple[int, int]:
+    """(seed, offset) of the device's default CUDA generator, whose offset is then advanced by
+    `count` rounded up to a multiple of 4: the bookkeeping of the reference
+    (flash_attention_triton.py:641-665), so that manual_seed() followed by the same sequence of
+    calls gives the same masks."""
+    state = torch.cuda.get_rng_state(device)
+    words = state.numpy().view("uint64")  # the last two words are the seed and the offset
+    seed, offset = int(words[-2]), int(words[-1])
+    words[-1] += ((int(count) + 3) // 4) * 4
+    torch.cuda.set_rng_state(state, device)
+    return seed, offset
+
+
+def dropout_mask(dropout_p: float, batch: int, heads: int, seqlen_q: int, seqlen_k: int, device,
+                 rng: Optional[Tuple[int, int]] = None) -> Tensor:
+    """Boolean (B, H, M, N) keep mask of the attention dropout; with `rng=None` it draws (seed,
+    offset) from the device's generator exactly as an attention call would
+    (triton_dropout_mask, flash_attention_triton.py:699-717)."""
+    device = torch.device(device)
+    if device.type != "cuda":
+        raise RuntimeError("dropout_mask needs a CUDA device (there is no CPU path)")
+    if device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    seed, offset = rng if rng is not None else next_dropout_rng(device, batch * heads * seqlen_q * seqlen_k)
+    out = torch.empty((batch, heads, seqlen_q, seqlen_k), dtype=torch.uint8, device=device)
+    rc = _lib.load().fo_dropout_mask(out.data_ptr(), batch, heads, seqlen_q, seqlen_k, float(dropout_p),
+                                     seed & (2**64 - 1), offset & (2**64 - 1), device.index,
+                                     _lib.current_stream_ptr(device))
+    _lib.check(rc)
+    return out.bool()
+
+
 def flash_attention_forward(Q: Tensor, K: Tensor, V: Tensor, *, causal: bool = False,
                             softmax_scale: Optional[float] = None,
                             return_lse: bool = False,
-                            out: Optional[Tensor] = None) -> Union[Tensor, Tuple[Tensor, Tensor]]:
-    """O = softmax(scale * Q K^T [+ causal mask]) V on the CUDA device holding Q.
+                            out: Optional[Tensor] = None,
+                            bias: Optional[Tensor] = None,
+                            dropout_p: float = 0.0,
+                            rng: Optional[Tuple[int, int]] = None) -> Union[Tensor, Tuple[Tensor, Tensor]]:
+    """O = softmax(scale * Q K^T [+ bias] [+ causal mask]) V on the CUDA device holding Q.
+
+    `bias`: 4-D, fp32 or Q's dtype, last two dimensions (1, N) or (M, N), the first two 1 or
+    (B, H); -inf entries mask.  `dropout_p` > 0 drops attention probabilities with the reference's
+    counter-based mask; `rng` = (seed, offset) must then be given (see `next_dropout_rng`).
 
     Q: (B, H, M, D); K, V: (B, H, N, D); fp16 or bf16; D in {64, 128}; the last dimension
     contiguous, the others with strides that are multiples of 8 elements (so (B, S, H, D)
@@ -70,19 +131,39 @@ def flash_attention_forward(Q: Tensor, K: Tensor, V: Tensor, *, causal: bool = F
         O = out
     lse = torch.empty((B, H, M), dtype=torch.float32, device=Q.device) if return_lse else None
     lib = _lib.load()
-    rc = lib.fo_flash_attn_fwd(
-        Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(), lse.data_ptr() if return_lse else None,
-        B, H, M, N, D, _strides3(Q), _strides3(K), _strides3(V), _strides3(O),
-        _lib.dtype_code(Q.dtype), int(bool(causal)), scale, Q.device.index,
-        _lib.current_stream_ptr(Q.device))
+    if bias is None and dropout_p == 0.0:
+        rc = lib.fo_flash_attn_fwd(
+            Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(), lse.data_ptr() if return_lse else None,
+            B, H, M, N, D, _strides3(Q), _strides3(K), _strides3(V), _strides3(O),
+            _lib.dtype_code(Q.dtype), int(bool(causal)), scale, Q.device.index,
+            _lib.current_stream_ptr(Q.device))
+    else:
+        if not 0.0 <= dropout_p < 1.0:
+            raise RuntimeError(f"dropout_p must be in [0, 1), got {dropout_p}")
+        if dropout_p > 0.0 and rng is None:
+            raise RuntimeError("dropout needs rng=(seed, offset); see next_dropout_rng")
+        seed, offset = rng if rng is not None else (0, 0)
+        bias_t, bias_ptr, bias_strides, bias_code = _prepare_bias(bias, Q, N)
+        rc = lib.fo_flash_attn_fwd_ex(
+            Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(), lse.data_ptr() if return_lse else None,
+            B, H, M, N, D, _strides3(Q), _strides3(K), _strides3(V), _strides3(O),
+            _lib.dtype_code(Q.dtype), int(bool(causal)), scale,
+            bias_ptr, bias_strides, bias_code, float(dropout_p), seed & (2**64 - 1), offset & (2**64 - 1),
+            Q.device.index, _lib.current_stream_ptr(Q.device))
     _lib.check(rc)
     return (O, lse) if return_lse else O
 
 
 def flash_attention_backward(dO: Tensor, Q: Tensor, K: Tensor, V: Tensor, O: Tensor, LSE: Tensor, *,
                              causal: bool = False,
-                             softmax_scale: Optional[float] = None) -> Tuple[Tensor, Tensor, Tensor]:
+                             softmax_scale: Optional[float] = None,
+                             bias: Optional[Tensor] = None,
+                             dropout_p: float = 0.0,
+                             rng: Optional[Tuple[int, int]] = None) -> Tuple[Tensor, Tensor, Tensor]:
     """(dQ, dK, dV) for the output gradient dO, from the forward's inputs, output O and LSE.
+
+    `bias`, `dropout_p` and `rng` must be those of the forward call; no gradient is produced for
+    the bias (as in the reference, flash_attention_triton.py:854).
 
     Shapes and dtypes as in `flash_attention_forward`; LSE is the (B, H, M) fp32 tensor that call
     returns with `return_lse=True`.  Semantics of the reference's complete backward
@@ -113,12 +194,26 @@ def flash_attention_backward(dO: Tensor, Q: Tensor, K: Tensor, V: Tensor, O: Ten
     dq_accum = torch.empty((B, H, M, D), dtype=torch.float32, device=Q.device)
     delta = torch.empty((B, H, M), dtype=torch.float32, device=Q.device)
     lib = _lib.load()
-    rc = lib.fo_flash_attn_bwd(
-        Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(), dO.data_ptr(), LSE.data_ptr(),
-        dQ.data_ptr(), dK.data_ptr(), dV.data_ptr(), dq_accum.data_ptr(), delta.data_ptr(),
-        B, H, M, N, D, _strides3(Q), _strides3(K), _strides3(V), _strides3(O), _strides3(dO),
-        _strides3(dQ), _strides3(dK), _strides3(dV),
-        _lib.dtype_code(Q.dtype), int(bool(causal)), scale, Q.device.index, _lib.current_stream_ptr(Q.device))
+    if bias is None and dropout_p == 0.0:
+        rc = lib.fo_flash_attn_bwd(
+            Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(), dO.data_ptr(), LSE.data_ptr(),
+            dQ.data_ptr(), dK.data_ptr(), dV.data_ptr(), dq_accum.data_ptr(), delta.data_ptr(),
+            B, H, M, N, D, _strides3(Q), _strides3(K), _strides3(V), _strides3(O), _strides3(dO),
+            _strides3(dQ), _strides3(dK), _strides3(dV),
+            _lib.dtype_code(Q.dtype), int(bool(causal)), scale, Q.device.index, _lib.current_stream_ptr(Q.device))
+    else:
+        if dropout_p > 0.0 and rng is None:
+            raise RuntimeError("dropout needs the forward's rng=(seed, offset)")
+        seed, offset = rng if rng is not None else (0, 0)
+        bias_t, bias_ptr, bias_strides, bias_code = _prepare_bias(bias, Q, N)
+        rc = lib.fo_flash_attn_bwd_ex(
+            Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(), dO.data_ptr(), LSE.data_ptr(),
+            dQ.data_ptr(), dK.data_ptr(), dV.data_ptr(), dq_accum.data_ptr(), delta.data_ptr(),
+            B, H, M, N, D, _strides3(Q), _strides3(K), _strides3(V), _strides3(O), _strides3(dO),
+            _strides3(dQ), _strides3(dK), _strides3(dV),
+            _lib.dtype_code(Q.dtype), int(bool(causal)), scale,
+            bias_ptr, bias_strides, bias_code, float(dropout_p), seed & (2**64 - 1), offset & (2**64 - 1),
+            Q.device.index, _lib.current_stream_ptr(Q.device))
     _lib.check(rc)
     return dQ, dK, dV
 
@@ -127,21 +222,30 @@ class _AttentionFunction(Function):
     """Forward + backward with the keyword arguments carried as non-tensor inputs."""
 
     @staticmethod
-    def forward(ctx, Q: Tensor, K: Tensor, V: Tensor, causal: bool, softmax_scale: Optional[float]):
-        O, lse = flash_attention_forward(Q, K, V, causal=causal, softmax_scale=softmax_scale, return_lse=True)
-        ctx.save_for_backward(Q, K, V, O, lse)
-        ctx.causal, ctx.softmax_scale = causal, softmax_scale
+    def forward(ctx, Q: Tensor, K: Tensor, V: Tensor, causal: bool, softmax_scale: Optional[float],
+                bias: Optional[Tensor], dropout_p: float):
+        rng = None
+        if dropout_p > 0.0:
+            # one index per attention probability (flash_attention_triton.py:780)
+            rng = next_dropout_rng(Q.device, Q.shape[0] * Q.shape[1] * Q.shape[2] * K.shape[2])
+        O, lse = flash_attention_forward(Q, K, V, causal=causal, softmax_scale=softmax_scale, return_lse=True,
+                                         bias=bias, dropout_p=dropout_p, rng=rng)
+        ctx.save_for_backward(Q, K, V, O, lse, bias)
+        ctx.causal, ctx.softmax_scale, ctx.dropout_p, ctx.rng = causal, softmax_scale, dropout_p, rng
         ctx.mark_non_differentiable(lse)
         return O, lse
 
     @staticmethod
     def backward(ctx, dO: Tensor, _dlse):
-        Q, K, V, O, lse = ctx.saved_tensors
+        Q, K, V, O, lse, bias = ctx.saved_tensors
+        if bias is not None and ctx.needs_input_grad[5]:
+            raise RuntimeError("attention bias gradient is not supported")  # flash_attention_triton.py:854
         if dO.stride(3) != 1:
             dO = dO.contiguous()
         dQ, dK, dV = flash_attention_backward(dO, Q, K, V, O, lse, causal=ctx.causal,
-                                              softmax_scale=ctx.softmax_scale)
-        return dQ, dK, dV, None, None
+                                              softmax_scale=ctx.softmax_scale, bias=bias,
+                                              dropout_p=ctx.dropout_p, rng=ctx.rng)
+        return dQ, dK, dV, None, None, None, None
 
 
 class FlashAttentionFunction(Function):
@@ -164,7 +268,9 @@ class FlashAttentionFunction(Function):
 
 def multi_head_attention(Q: Tensor, K: Tensor, V: Tensor, *, causal: bool = False,
                          softmax_scale: Optional[float] = None,
-                         return_lse: bool = False) -> Union[Tensor, Tuple[Tensor, Tensor]]:
+                         return_lse: bool = False,
+                         bias: Optional[Tensor] = None,
+                         dropout_p: float = 0.0) -> Union[Tensor, Tuple[Tensor, Tensor]]:
     """Drop-in for fast_ops.flash_attention.flash_attention.multi_head_attention (:48-77).
 
     :param Q: (B, H, M, D) query.  :param K: (B, H, N, D) key.  :param V: (B, H, N, D) value.
@@ -172,11 +278,16 @@ def multi_head_attention(Q: Tensor, K: Tensor, V: Tensor, *, causal: bool = Fals
 
     Limitations (violations raise RuntimeError): head_dim 64 or 128 in this build (the
     reference states <= 128 and a multiple of 8); fp16 / bf16 inputs; last dimension
-    contiguous.  The scale is 1/sqrt(D) unless `softmax_scale` is given.
+    contiguous.  The scale is 1/sqrt(D) unless `softmax_scale` is given.  `bias` and `dropout_p`
+    as in `flash_attention_forward`; the dropout mask is drawn from the device's default generator.
     """
-    if not causal and softmax_scale is None and not return_lse:
+    if not causal and softmax_scale is None and not return_lse and bias is None and dropout_p == 0.0:
         return FlashAttentionFunction.apply(Q, K, V)
     if torch.is_grad_enabled() and (Q.requires_grad or K.requires_grad or V.requires_grad):
-        O, lse = _AttentionFunction.apply(Q, K, V, bool(causal), softmax_scale)
+        O, lse = _AttentionFunction.apply(Q, K, V, bool(causal), softmax_scale, bias, float(dropout_p))
         return (O, lse) if return_lse else O
-    return flash_attention_forward(Q, K, V, causal=causal, softmax_scale=softmax_scale, return_lse=return_lse)
+    rng = None
+    if dropout_p > 0.0:
+        rng = next_dropout_rng(Q.device, Q.shape[0] * Q.shape[1] * Q.shape[2] * K.shape[2])
+    return flash_attention_forward(Q, K, V, causal=causal, softmax_scale=softmax_scale, return_lse=return_lse,
+                                   bias=bias, dropout_p=float(dropout_p), rng=rng)

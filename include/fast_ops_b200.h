@@ -79,7 +79,7 @@ int fo_flash_attn_fwd(const void* q, const void* k, const void* v, void* o, floa
  * batch/head/sequence strides.  `dq_accum` (B*H*Sq*D floats) and `delta` (B*H*Sq floats) are
  * scratch the caller provides; their contents on entry do not matter.  Three launches on `stream`:
  * delta = rowsum(O o dO), the main kernel (dK, dV per key tile; dQ added into dq_accum with
- * atomics, so dQ may differ in the last bit between runs), and the rounding of dq_accum into dq.
+ * bulk reduce-adds, so dQ may differ in the last bit between runs), and the rounding of dq_accum into dq.
  */
 int fo_flash_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout,
                       const float* lse, void* dq, void* dk, void* dv, float* dq_accum, float* delta,
@@ -88,6 +88,56 @@ int fo_flash_attn_bwd(const void* q, const void* k, const void* v, const void* o
                       const int64_t o_strides[3], const int64_t do_strides[3],
                       const int64_t dq_strides[3], const int64_t dk_strides[3], const int64_t dv_strides[3],
                       int dtype, int causal, float softmax_scale, int device, void* stream);
+
+/*
+ * FlashAttention forward and backward with the additive bias and the dropout of the reference's
+ * complete implementation (forward: fast_ops/flash_attention/flash_attention_triton.py:176-199
+ * bias, :215-219 dropout; backward: :496-510, :517-551, :580-603).  The arguments up to
+ * softmax_scale are those of fo_flash_attn_fwd / fo_flash_attn_bwd.
+ *
+ *   bias         : NULL, or a device pointer to values added to softmax_scale * Q K^T before the
+ *                  softmax: element (b, h, i, j) at bias + b*s[0] + h*s[1] + i*s[2] + j with
+ *                  s = bias_strides in elements; a stride of 0 broadcasts that dimension (the
+ *                  reference's "vector" bias is s[2] = 0, flash_attention_triton.py:760-769).
+ *                  -inf entries mask; a row whose entries are all masked gets O = 0 and
+ *                  LSE = -inf (the torch oracle gives NaN there).  No gradient is produced for
+ *                  the bias, as in the reference (flash_attention_triton.py:854).
+ *   bias_dtype   : FO_F32, or the dtype of q (flash_attention_triton.py:755).
+ *   dropout_p    : in [0, 1).  Element (i, j) of head (b, h) is kept iff
+ *                  hash((uint32)(rng_offset + ((b*H + h)*Sq + i)*Sk + j) ^ (uint32)rng_seed) >
+ *                  (uint32)(dropout_p * 2^32) with the integer hash of
+ *                  flash_attention_triton.py:38-50; kept probabilities are scaled by
+ *                  1 / (1 - dropout_p) in P V, the row sums and LSE are those without dropout.
+ *                  The backward must be given the forward's p, seed and offset.
+ */
+int fo_flash_attn_fwd_ex(const void* q, const void* k, const void* v, void* o, float* lse,
+                         int B, int H, int Sq, int Sk, int D,
+                         const int64_t q_strides[3], const int64_t k_strides[3],
+                         const int64_t v_strides[3], const int64_t o_strides[3],
+                         int dtype, int causal, float softmax_scale,
+                         const void* bias, const int64_t bias_strides[3], int bias_dtype,
+                         float dropout_p, uint64_t rng_seed, uint64_t rng_offset,
+                         int device, void* stream);
+
+int fo_flash_attn_bwd_ex(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                         const float* lse, void* dq, void* dk, void* dv, float* dq_accum, float* delta,
+                         int B, int H, int Sq, int Sk, int D,
+                         const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
+                         const int64_t o_strides[3], const int64_t do_strides[3],
+                         const int64_t dq_strides[3], const int64_t dk_strides[3], const int64_t dv_strides[3],
+                         int dtype, int causal, float softmax_scale,
+                         const void* bias, const int64_t bias_strides[3], int bias_dtype,
+                         float dropout_p, uint64_t rng_seed, uint64_t rng_offset,
+                         int device, void* stream);
+
+/*
+ * Materialises the keep mask of the dropout above as B*H*Sq*Sk bytes (1 = kept), dense in
+ * (b, h, i, j) order.  Replaces triton_dropout_mask / _dropout_mask_kernel
+ * (fast_ops/flash_attention/flash_attention_triton.py:668-717), which the reference's tests use
+ * to build the oracle's mask.
+ */
+int fo_dropout_mask(uint8_t* out, int B, int H, int Sq, int Sk, float dropout_p, uint64_t rng_seed,
+                    uint64_t rng_offset, int device, void* stream);
 
 /*
  * Fused Lion step on one dense tensor, in place:

@@ -6,8 +6,10 @@ leg of bench.py as the checker / timed CPU reference.  The product package
 """
 from .oracle import (  # noqa: F401
     attention_bwd,
+    attention_ex,
     attention_fwd,
     build,
+    dropout_mask,
     lion_step,
     num_threads,
     set_num_threads,

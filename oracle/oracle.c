@@ -389,3 +389,174 @@ void oracle_attention_bwd(const float* q, const float* k, const float* v, const 
   parallel_for((int64_t)(bh_end - bh_begin) * Sq, 8, attn_bwd_rows, &ctx);
   parallel_for((int64_t)(bh_end - bh_begin) * Sk, 8, attn_bwd_keys, &ctx);
 }
+
+/* ---- attention with bias and dropout -------------------------------------------------------
+ * fast_ops/flash_attention/attention_ref.py:41-67 with its optional arguments:
+ *   scores = (q / sqrt(d)) k^T;  scores += bias (:50-51);  causal triu(.,1) -> -inf (:54-58);
+ *   attention = softmax(scores) (:59);  dropped entries -> 0 (:63-64);
+ *   out = attention_drop (v / (1 - p)) (:67).
+ * bias: fp32, element (b,h,i,j) at bias[b*sb + h*sh + i*sq + j] (0 strides broadcast), or NULL.
+ * keep: dense (B,H,Sq,Sk) bytes, 1 = kept, or NULL.  A row whose scores are all -inf gives NaN,
+ * as torch's softmax does.
+ * The backward is what autograd computes through the same lines:
+ *   Z = keep / (1 - p);  dV = (P o Z)^T dO;  dP = (dO V^T) o Z;
+ *   dS = P o (dP - rowsum(dP o P)) * scale;  dQ = dS K;  dK = dS^T Q.
+ *
+ * oracle_dropout_mask restates the keep decision of
+ * fast_ops/flash_attention/flash_attention_triton.py:38-50 with the element index of :125, :217
+ * (all arithmetic modulo 2^32; the threshold is the fp32 product p * 2^32 truncated). */
+static uint32_t dropout_hash(uint32_t idx, uint32_t seed) {
+  uint32_t a = idx ^ seed;
+  a ^= a >> 4;
+  a = (a ^ 0xDEADBEEFu) + (a << 5);
+  a ^= a >> 11;
+  return a;
+}
+
+void oracle_dropout_mask(uint8_t* keep, int64_t total, float dropout_p, uint64_t seed, uint64_t offset) {
+  const float prod = dropout_p * 4294967296.0f;
+  const uint32_t thr = prod >= 4294967296.0f ? 0xffffffffu : (uint32_t)prod;
+  for (int64_t i = 0; i < total; ++i)
+    keep[i] = dropout_hash((uint32_t)offset + (uint32_t)i, (uint32_t)seed) > thr ? 1 : 0;
+}
+
+typedef struct {
+  const float *q, *k, *v, *dout, *bias;
+  const uint8_t* keep;
+  float *out, *dq, *dk, *dv, *lse, *delta;
+  int64_t bias_sb, bias_sh, bias_sq;
+  int H, Sq, Sk, D, causal;
+  float scale, rescale;
+} attn_ex_ctx;
+
+/* scaled, biased and masked score of (row i, key j) */
+static float ex_score(const attn_ex_ctx* c, int bh, int i, int j) {
+  if (c->causal && j > i) return -INFINITY;
+  const float* qi = c->q + ((int64_t)bh * c->Sq + i) * c->D;
+  const float* kj = c->k + ((int64_t)bh * c->Sk + j) * c->D;
+  float s = 0.f;
+#pragma omp simd reduction(+ : s)
+  for (int d = 0; d < c->D; ++d) s += (qi[d] * c->scale) * kj[d];
+  if (c->bias) {
+    const int b = bh / c->H, h = bh % c->H;
+    s += c->bias[b * c->bias_sb + h * c->bias_sh + (int64_t)i * c->bias_sq + j];
+  }
+  return s;
+}
+
+static void attn_ex_rows(int64_t begin, int64_t end, void* vctx) {
+  const attn_ex_ctx* c = (const attn_ex_ctx*)vctx;
+  const int Sq = c->Sq, Sk = c->Sk, D = c->D;
+  float* p = (float*)malloc(sizeof(float) * (size_t)Sk);
+  float* acc = (float*)malloc(sizeof(float) * (size_t)D);
+  for (int64_t r = begin; r < end; ++r) {
+    const int bh = (int)(r / Sq), i = (int)(r % Sq);
+    const uint8_t* keep = c->keep ? c->keep + ((int64_t)bh * Sq + i) * Sk : NULL;
+    const float* vb = c->v + (int64_t)bh * Sk * D;
+    const float* kb = c->k + (int64_t)bh * Sk * D;
+    float mx = -INFINITY;
+    for (int j = 0; j < Sk; ++j) {
+      p[j] = ex_score(c, bh, i, j);
+      if (p[j] > mx) mx = p[j];
+    }
+    float sum = 0.f;
+    for (int j = 0; j < Sk; ++j) {
+      p[j] = expf(p[j] - mx);
+      sum += p[j];
+    }
+    const float inv = 1.f / sum;
+    for (int j = 0; j < Sk; ++j) p[j] *= inv;
+    for (int d = 0; d < D; ++d) acc[d] = 0.f;
+    for (int j = 0; j < Sk; ++j) {
+      if (keep && !keep[j]) continue;
+      const float* vj = vb + (int64_t)j * D;
+      for (int d = 0; d < D; ++d) acc[d] += p[j] * (vj[d] * c->rescale);
+    }
+    if (c->out) {
+      float* oi = c->out + ((int64_t)bh * Sq + i) * D;
+      for (int d = 0; d < D; ++d) oi[d] = acc[d];
+    }
+    if (c->lse) c->lse[(int64_t)bh * Sq + i] = mx + logf(sum);
+    if (c->dout) {
+      const float* doi = c->dout + ((int64_t)bh * Sq + i) * D;
+      float delta = 0.f;
+      for (int d = 0; d < D; ++d) delta += acc[d] * doi[d];
+      c->delta[(int64_t)bh * Sq + i] = delta;
+      for (int d = 0; d < D; ++d) acc[d] = 0.f;
+      for (int j = 0; j < Sk; ++j) {
+        float dp = 0.f;
+        if (!keep || keep[j]) {
+          const float* vj = vb + (int64_t)j * D;
+          for (int d = 0; d < D; ++d) dp += doi[d] * vj[d];
+          dp *= c->rescale;
+        }
+        const float ds = p[j] * (dp - delta) * c->scale;
+        const float* kj = kb + (int64_t)j * D;
+        for (int d = 0; d < D; ++d) acc[d] += ds * kj[d];
+      }
+      float* dqi = c->dq + ((int64_t)bh * Sq + i) * D;
+      for (int d = 0; d < D; ++d) dqi[d] = acc[d];
+    }
+  }
+  free(p);
+  free(acc);
+}
+
+static void attn_ex_keys(int64_t begin, int64_t end, void* vctx) {
+  const attn_ex_ctx* c = (const attn_ex_ctx*)vctx;
+  const int Sq = c->Sq, Sk = c->Sk, D = c->D;
+  float* ak = (float*)malloc(sizeof(float) * (size_t)D);
+  float* av = (float*)malloc(sizeof(float) * (size_t)D);
+  for (int64_t r = begin; r < end; ++r) {
+    const int bh = (int)(r / Sk), j = (int)(r % Sk);
+    const float* vj = c->v + ((int64_t)bh * Sk + j) * D;
+    for (int d = 0; d < D; ++d) ak[d] = av[d] = 0.f;
+    for (int i = 0; i < Sq; ++i) {
+      const float lse = c->lse[(int64_t)bh * Sq + i];
+      const float s = ex_score(c, bh, i, j);
+      if (s == -INFINITY) continue;
+      const float p = expf(s - lse);
+      const int kept = !c->keep || c->keep[((int64_t)bh * Sq + i) * Sk + j];
+      const float* qi = c->q + ((int64_t)bh * Sq + i) * D;
+      const float* doi = c->dout + ((int64_t)bh * Sq + i) * D;
+      float dp = 0.f;
+      if (kept) {
+        for (int d = 0; d < D; ++d) dp += doi[d] * vj[d];
+        dp *= c->rescale;
+      }
+      const float ds = p * (dp - c->delta[(int64_t)bh * Sq + i]) * c->scale;
+      for (int d = 0; d < D; ++d) {
+        if (kept) av[d] += (p * c->rescale) * doi[d];
+        ak[d] += ds * qi[d];
+      }
+    }
+    float* dkj = c->dk + ((int64_t)bh * Sk + j) * D;
+    float* dvj = c->dv + ((int64_t)bh * Sk + j) * D;
+    for (int d = 0; d < D; ++d) {
+      dkj[d] = ak[d];
+      dvj[d] = av[d];
+    }
+  }
+  free(ak);
+  free(av);
+}
+
+/* Forward only when dout is NULL (dq, dk, dv, delta then unused); lse is required for the
+ * backward (scratch of B*H*Sq floats) and optional otherwise. */
+void oracle_attention_ex(const float* q, const float* k, const float* v, const float* bias,
+                         const int64_t* bias_strides, const uint8_t* keep, float dropout_p,
+                         float* out, float* lse, const float* dout, float* dq, float* dk, float* dv,
+                         float* delta, int B, int H, int Sq, int Sk, int D, int causal, float scale) {
+  if (B <= 0 || H <= 0 || Sq <= 0 || Sk <= 0) return;
+  attn_ex_ctx c;
+  memset(&c, 0, sizeof(c));
+  c.q = q; c.k = k; c.v = v; c.dout = dout; c.bias = bias; c.keep = keep;
+  c.out = out; c.dq = dq; c.dk = dk; c.dv = dv; c.lse = lse; c.delta = delta;
+  if (bias) { c.bias_sb = bias_strides[0]; c.bias_sh = bias_strides[1]; c.bias_sq = bias_strides[2]; }
+  c.H = H; c.Sq = Sq; c.Sk = Sk; c.D = D; c.causal = causal;
+  c.scale = scale;
+  c.rescale = keep ? 1.0f / (1.0f - dropout_p) : 1.0f;
+  parallel_for((int64_t)B * H * Sq, 8, attn_ex_rows, &c);
+  if (dout) parallel_for((int64_t)B * H * Sk, 8, attn_ex_keys, &c);
+}
+

@@ -44,6 +44,12 @@ def _load() -> ctypes.CDLL:
         lib.oracle_attention_bwd.argtypes = [ctypes.c_void_p] * 9 + [ctypes.c_int] * 6 + [
             ctypes.c_float, ctypes.c_int, ctypes.c_int]
         lib.oracle_attention_bwd.restype = None
+        lib.oracle_attention_ex.argtypes = [ctypes.c_void_p] * 6 + [ctypes.c_float] + [ctypes.c_void_p] * 7 + [
+            ctypes.c_int] * 6 + [ctypes.c_float]
+        lib.oracle_attention_ex.restype = None
+        lib.oracle_dropout_mask.argtypes = [ctypes.c_void_p, ctypes.c_int64, ctypes.c_float, ctypes.c_uint64,
+                                            ctypes.c_uint64]
+        lib.oracle_dropout_mask.restype = None
         lib.oracle_num_threads.restype = ctypes.c_int
         lib.oracle_set_num_threads.argtypes = [ctypes.c_int]
         _lib = lib
@@ -119,3 +125,56 @@ def attention_bwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, dout: torch
                                  dk.data_ptr(), dv.data_ptr(), lse.data_ptr(), delta.data_ptr(), B, H, Sq, Sk, D,
                                  int(bool(causal)), float(softmax_scale), int(b), int(e))
     return dq, dk, dv
+
+
+def dropout_mask(dropout_p: float, B: int, H: int, Sq: int, Sk: int, seed: int, offset: int) -> torch.Tensor:
+    """Boolean (B,H,Sq,Sk) keep mask of the reference's attention dropout
+    (fast_ops/flash_attention/flash_attention_triton.py:38-50 with the indices of :125, :217)."""
+    keep = torch.empty(B, H, Sq, Sk, dtype=torch.uint8)
+    _load().oracle_dropout_mask(keep.data_ptr(), keep.numel(), float(dropout_p), seed & (2**64 - 1),
+                                offset & (2**64 - 1))
+    return keep.bool()
+
+
+def attention_ex(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, bias: Optional[torch.Tensor] = None,
+                 keep_mask: Optional[torch.Tensor] = None, dropout_p: float = 0.0, causal: bool = False,
+                 softmax_scale: Optional[float] = None, dout: Optional[torch.Tensor] = None):
+    """Attention with additive bias and dropout in fp32 on the CPU
+    (fast_ops/flash_attention/attention_ref.py:41-67 with `bias` and `dropout_mask`).
+
+    q: (B,H,Sq,D), k/v: (B,H,Sk,D); bias broadcastable to (B,H,Sq,Sk); keep_mask boolean
+    (B,H,Sq,Sk).  Returns (out, lse), or (out, lse, dq, dk, dv) when `dout` is given.
+    """
+    B, H, Sq, D = q.shape
+    Sk = k.shape[2]
+    if softmax_scale is None:
+        softmax_scale = 1.0 / (D ** 0.5)
+    qf, kf, vf = (t.detach().to("cpu", torch.float32).contiguous() for t in (q, k, v))
+    out = torch.zeros(B, H, Sq, D)
+    lse = torch.zeros(B, H, Sq)
+    bias_ptr, strides = None, None
+    if bias is not None:
+        bf = bias.detach().to("cpu", torch.float32)
+        if bf.stride(-1) != 1:
+            bf = bf.contiguous()
+        bf = bf.expand(B, H, Sq, Sk)
+        bias_ptr = bf.data_ptr()
+        strides = (ctypes.c_int64 * 3)(bf.stride(0), bf.stride(1), bf.stride(2))
+    keep_ptr = None
+    if keep_mask is not None:
+        km = keep_mask.detach().to("cpu", torch.uint8).expand(B, H, Sq, Sk).contiguous()
+        keep_ptr = km.data_ptr()
+    if dout is None:
+        _load().oracle_attention_ex(qf.data_ptr(), kf.data_ptr(), vf.data_ptr(), bias_ptr, strides, keep_ptr,
+                                    float(dropout_p), out.data_ptr(), lse.data_ptr(), None, None, None, None, None,
+                                    B, H, Sq, Sk, D, int(bool(causal)), float(softmax_scale))
+        return out, lse
+    df = dout.detach().to("cpu", torch.float32).contiguous()
+    dq, dk, dv = torch.zeros_like(qf), torch.zeros_like(kf), torch.zeros_like(vf)
+    delta = torch.zeros(B, H, Sq)
+    _load().oracle_attention_ex(qf.data_ptr(), kf.data_ptr(), vf.data_ptr(), bias_ptr, strides, keep_ptr,
+                                float(dropout_p), out.data_ptr(), lse.data_ptr(), df.data_ptr(), dq.data_ptr(),
+                                dk.data_ptr(), dv.data_ptr(), delta.data_ptr(),
+                                B, H, Sq, Sk, D, int(bool(causal)), float(softmax_scale))
+    return out, lse, dq, dk, dv
+

@@ -2,7 +2,7 @@
 
 Run once, in a container where the reference checkout is importable:
 
-    python tests/golden/make_golden.py /path/to/fast-ops [attention|attention_bwd|lion]
+    python tests/golden/make_golden.py /path/to/fast-ops [attention|attention_bwd|attention_ex|lion]
 
 It imports fast_ops.flash_attention.attention_ref.attention_ref and
 fast_ops.lion.lion_optimizer_ref.Lion from that checkout, feeds them seeded inputs and stores
@@ -109,6 +109,83 @@ def make_attention_bwd(attention_ref):
         print("attention backward", name)
 
 
+def reference_dropout_mask(ref_root, dropout_p, B, H, Sq, Sk, seed, offset):
+    """Keep mask from the reference's own _dropout_mask_kernel
+    (fast_ops/flash_attention/flash_attention_triton.py:668-696), run on the CPU by Triton's
+    interpreter (TRITON_INTERPRET=1 is set in main() before triton is imported).  The
+    interpreter leaves a Python float argument a float, on which the kernel's `.to()` fails, so
+    dropout_p is handed over as the fp32 scalar the compiled kernel would receive."""
+    import importlib.util
+
+    import triton
+    import triton.language as tl
+    from triton.runtime.interpreter import TensorHandle
+
+    spec = importlib.util.spec_from_file_location(
+        "ref_flash_attention_triton", os.path.join(ref_root, "fast_ops/flash_attention/flash_attention_triton.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    p32 = tl.tensor(TensorHandle(np.array([dropout_p], dtype=np.float32), tl.float32), tl.float32)
+    t = torch.empty((B, H, Sq, Sk), dtype=torch.int32)
+    grid = (triton.cdiv(Sq, 128), B * H)
+    mod._dropout_mask_kernel[grid](t, p32, Sq, Sk, seed, offset, 128, 128)
+    return t.to(torch.bool)
+
+
+def attention_ex_inputs(seed, B, H, Sq, Sk, D, dtype, bias_code):
+    """Q, K, V as attention_inputs; dO and the fp32 bias from a second seeded generator.  The
+    bias gets a few -inf (masking) entries, never a whole row."""
+    q, k, v = attention_inputs(seed, B, H, Sq, Sk, D, dtype)
+    gen = torch.Generator().manual_seed(seed + 1000)
+    dout = torch.randn(B, H, Sq, D, generator=gen).to(dtype)
+    bias = None
+    if bias_code is not None:
+        shape = {"1h1k": (1, H, 1, Sk), "1hqk": (1, H, Sq, Sk), "b11k": (B, 1, 1, Sk), "b1qk": (B, 1, Sq, Sk)}[bias_code]
+        bias = torch.randn(shape, generator=gen)
+        bias[..., 3::17] = float("-inf")
+    return q, k, v, dout, bias
+
+
+def make_attention_ex(attention_ref, ref_root):
+    """Forward and autograd gradients of attention_ref with a bias and / or a dropout mask
+    (fast_ops/flash_attention/attention_ref.py:50-51, :60-67), the mask made by the reference's
+    mask kernel.  The reference's hash keeps or drops runs of up to ~10^6 consecutive element
+    indices, so the offsets below are chosen next to a boundary of such a run (found by
+    evaluating the hash) to get masks that contain both kept and dropped elements."""
+    cases = [
+        # name, seed, B, H, Sq, Sk, D, dtype, causal, bias shape code, dropout_p, rng seed, rng offset
+        ("bias1h1k_s200d64_bf16_causal", 21, 2, 2, 200, 200, 64, "bf16", True, "1h1k", 0.0, 0, 0),
+        ("biasb1qk_sq130sk300d128_f16_full", 22, 2, 2, 130, 300, 128, "f16", False, "b1qk", 0.0, 0, 0),
+        ("bias1hqk_s256d128_bf16_causal", 23, 1, 2, 256, 256, 128, "bf16", True, "1hqk", 0.0, 0, 0),
+        ("drop_s256d64_bf16_full", 24, 2, 2, 256, 256, 64, "bf16", False, None, 0.17, 0, 16646144),
+        ("drop_biasb11k_s200d128_f16_causal", 25, 2, 3, 200, 200, 128, "f16", True, "b11k", 0.17, 0, 17700000),
+    ]
+    for name, seed, B, H, Sq, Sk, D, dt, causal, bias_code, p, rseed, roff in cases:
+        q, k, v, dout, bias = attention_ex_inputs(seed, B, H, Sq, Sk, D, DT[dt], bias_code)
+        keep = None
+        if p > 0:
+            keep = reference_dropout_mask(ref_root, p, B, H, Sq, Sk, rseed, roff)
+            frac = keep.float().mean().item()
+            assert 0.05 < frac < 0.95, (name, frac)
+        qf, kf, vf = (t.float().transpose(1, 2).requires_grad_(True) for t in (q, k, v))
+        out, _ = attention_ref(qf, kf, vf, causal=causal, bias=bias, dropout_p=p, dropout_mask=keep, upcast=True)
+        out.backward(dout.float().transpose(1, 2))
+        rq, rk = np.arange(0, Sq, 3), np.arange(0, Sk, 3)  # stored sample of rows
+        np.savez_compressed(
+            os.path.join(HERE, f"attnex_{name}.npz"),
+            seed=seed, shape=np.array([B, H, Sq, Sk, D]), dtype=dt, causal=causal,
+            bias_code="" if bias_code is None else bias_code,
+            dropout_p=p, rng_seed=rseed, rng_offset=roff,
+            keep_packed=np.zeros(0, np.uint8) if keep is None else np.packbits(keep.numpy()),
+            input_sha256=digest(*([q, k, v, dout] + ([] if bias is None else [bias]))),
+            rows_q=rq, rows_k=rk,
+            out=out.detach().transpose(1, 2)[:, :, rq].contiguous().numpy(),
+            dq=qf.grad.transpose(1, 2)[:, :, rq].contiguous().numpy(),
+            dk=kf.grad.transpose(1, 2)[:, :, rk].contiguous().numpy(),
+            dv=vf.grad.transpose(1, 2)[:, :, rk].contiguous().numpy())
+        print("attention ex", name, "keep fraction", None if keep is None else round(frac, 3))
+
+
 def make_lion(LionRef):
     n = 2048
     cases = [
@@ -156,6 +233,7 @@ def make_lion(LionRef):
 
 def main():
     ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    os.environ["TRITON_INTERPRET"] = "1"  # the reference's mask kernel runs on the CPU
     sys.path.insert(0, ref_root)
     from fast_ops.flash_attention.attention_ref import attention_ref
     from fast_ops.lion.lion_optimizer_ref import Lion as LionRef
@@ -166,6 +244,8 @@ def main():
         make_attention(attention_ref)
     if only in ("all", "attention_bwd"):
         make_attention_bwd(attention_ref)
+    if only in ("all", "attention_ex"):
+        make_attention_ex(attention_ref, ref_root)
     if only in ("all", "lion"):
         make_lion(LionRef)
 

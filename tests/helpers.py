@@ -37,6 +37,33 @@ def attention_inputs(seed, B, H, Sq, Sk, D, dtype):
     return q, k, v
 
 
+def attention_ex_inputs(seed, B, H, Sq, Sk, D, dtype, bias_code):
+    """The generator's recipe for the bias / dropout cases: Q, K, V as above, dO and an fp32 bias
+    (with a few -inf entries) from a second seeded generator."""
+    q, k, v = attention_inputs(seed, B, H, Sq, Sk, D, dtype)
+    gen = torch.Generator().manual_seed(int(seed) + 1000)
+    dout = torch.randn(B, H, Sq, D, generator=gen).to(dtype)
+    bias = None
+    if bias_code:
+        shape = {"1h1k": (1, H, 1, Sk), "1hqk": (1, H, Sq, Sk), "b11k": (B, 1, 1, Sk), "b1qk": (B, 1, Sq, Sk)}[bias_code]
+        bias = torch.randn(shape, generator=gen)
+        bias[..., 3::17] = float("-inf")
+    return q, k, v, dout, bias
+
+
+def load_attention_ex_case(path):
+    """(golden dict, q, k, v, dout, bias, keep mask or None) of one attnex_*.npz file, with the
+    regenerated inputs checked against the stored digest."""
+    g = np.load(path)
+    B, H, Sq, Sk, D = (int(x) for x in g["shape"])
+    q, k, v, dout, bias = attention_ex_inputs(int(g["seed"]), B, H, Sq, Sk, D, DT[str(g["dtype"])], str(g["bias_code"]))
+    assert input_digest(*([q, k, v, dout] + ([] if bias is None else [bias]))) == str(g["input_sha256"])
+    keep = None
+    if float(g["dropout_p"]) > 0:
+        keep = torch.from_numpy(np.unpackbits(g["keep_packed"])[: B * H * Sq * Sk].reshape(B, H, Sq, Sk).astype(bool))
+    return g, q, k, v, dout, bias, keep
+
+
 def input_digest(*tensors) -> str:
     h = hashlib.sha256()
     for t in tensors:

@@ -43,3 +43,19 @@ def test_version_and_error_text_need_no_gpu():
     assert rc == -3 and b"head_dim 96" in lib.fo_last_error()
     rc = lib.fo_flash_attn_fwd(1, 1, 1, 1, None, 1, 1, 128, 128, 130, s, s, s, s, L.FO_BF16, 0, 0.1, 0, None)
     assert rc == -1
+
+
+def test_bias_and_dropout_arguments_are_validated_without_a_gpu():
+    lib = L.load()
+    s = (ctypes.c_int64 * 3)(0, 0, 0)
+    common = (1, 1, 1, 1, None, 1, 1, 128, 128, 64, s, s, s, s, L.FO_BF16, 0, 0.125)
+    rc = lib.fo_flash_attn_fwd_ex(*common, None, None, L.FO_F32, 1.0, 0, 0, 0, None)
+    assert rc == -1 and b"dropout_p" in lib.fo_last_error()
+    rc = lib.fo_flash_attn_fwd_ex(*common, 16, s, L.FO_F16, 0.0, 0, 0, 0, None)
+    assert rc == -1 and b"bias must be fp32" in lib.fo_last_error()
+    rc = lib.fo_flash_attn_fwd_ex(*common, 16, None, L.FO_F32, 0.0, 0, 0, 0, None)
+    assert rc == -1 and b"strides" in lib.fo_last_error()
+    rc = lib.fo_dropout_mask(None, 1, 1, 8, 8, 0.5, 0, 0, 0, None)
+    assert rc == -1
+    rc = lib.fo_dropout_mask(16, 1, 1, 8, 8, 0.0, 0, 0, 0, None)
+    assert rc == -1 and b"dropout_p" in lib.fo_last_error()

@@ -94,3 +94,50 @@ def test_attention_backward_oracle_matches_reference_autograd(path):
     for name, got in (("dq", dq), ("dk", dk), ("dv", dv)):
         want = torch.from_numpy(z[name])
         assert torch.allclose(got, want, atol=1e-5, rtol=1e-4), f"{name}: {(got - want).abs().max()}"
+
+
+@pytest.mark.parametrize("path", golden_files("attnex"), ids=lambda p: p.split("attnex_")[-1][:-4])
+def test_attention_bias_dropout_oracle_matches_reference(path):
+    """Bias and dropout: the oracle against attention_ref's forward and autograd gradients, and its
+    restatement of the keep mask, bit for bit, against the reference's own mask kernel."""
+    from helpers import load_attention_ex_case
+
+    g, q, k, v, dout, bias, keep = load_attention_ex_case(path)
+    B, H, Sq, Sk, D = (int(x) for x in g["shape"])
+    p = float(g["dropout_p"])
+    if keep is not None:
+        mine = oracle.dropout_mask(p, B, H, Sq, Sk, int(g["rng_seed"]), int(g["rng_offset"]))
+        assert torch.equal(mine, keep)
+        assert 0 < int(keep.sum()) < keep.numel()
+    out, lse, dq, dk, dv = oracle.attention_ex(q, k, v, bias=bias, keep_mask=keep, dropout_p=p,
+                                               causal=bool(g["causal"]), dout=dout)
+    rq, rk = g["rows_q"], g["rows_k"]
+    for name, got, rows in (("out", out, rq), ("dq", dq, rq), ("dk", dk, rk), ("dv", dv, rk)):
+        want = torch.from_numpy(g[name])
+        got = got[:, :, rows]
+        assert torch.allclose(got, want, atol=2e-5, rtol=1e-4), f"{name}: {(got - want).abs().max()}"
+    # forward-only entry gives the same output and LSE
+    out2, lse2 = oracle.attention_ex(q, k, v, bias=bias, keep_mask=keep, dropout_p=p, causal=bool(g["causal"]))
+    assert torch.equal(out2, out) and torch.equal(lse2, lse)
+
+
+def test_attention_ex_oracle_reduces_to_plain_attention():
+    q, k, v = attention_inputs(77, 1, 2, 70, 90, 64, torch.float32)
+    out, lse = oracle.attention_fwd(q, k, v, causal=True)
+    out2, lse2 = oracle.attention_ex(q, k, v, causal=True)
+    assert torch.allclose(out, out2, atol=1e-6) and torch.allclose(lse, lse2, atol=1e-6)
+
+
+def test_dropout_mask_oracle_statistics():
+    """The reference's statistical criterion (tests/test_flash_attention_triton.py:203-246: over
+    many generator offsets every element is kept about 1 - p of the time).  The hash keeps or
+    drops long runs of consecutive indices, so the offsets here are spread over the whole
+    32-bit index range instead of following one another."""
+    p, B, H, Sq, Sk = 0.17, 1, 2, 32, 128
+    trials = 2048
+    total = torch.zeros(B, H, Sq, Sk)
+    for t in range(trials):
+        total += oracle.dropout_mask(p, B, H, Sq, Sk, 0, t * (2**32 // trials))
+    frac = total / trials
+    assert abs(frac.mean().item() - (1 - p)) < 0.01
+    assert frac.min().item() > 0.75 and frac.max().item() < 0.91
