@@ -65,7 +65,7 @@ attn_bwd_finish_dq_kernel(const float* __restrict__ dq_accum, uint16_t* __restri
   *reinterpret_cast<uint4*>(dq + b * q_sb + h * q_sh + row * q_ss + d0) = v;
 }
 
-template <int D, bool kBf16, bool kExt>
+template <int D, bool kBf16, int kExt>
 int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
                const CUtensorMap& tdq, const fo::AttnBwdParams& prm, cudaStream_t stream) {
   auto kernel = fo::attn_bwd_kernel<D, kBf16, kExt>;
@@ -177,13 +177,20 @@ static int attn_bwd_impl(const void* q, const void* k, const void* v, const void
   const bool ext = ex != nullptr && (ex->bias != nullptr || ex->dropout);
   if (ext) prm.ex = *ex;
   int rc;
-  if (ext) {
-    if (D == 128) rc = bf16 ? launch_bwd<128, true, true>(tq, tk, tv, tdo, tdq, prm, s) : launch_bwd<128, false, true>(tq, tk, tv, tdo, tdq, prm, s);
-    else rc = bf16 ? launch_bwd<64, true, true>(tq, tk, tv, tdo, tdq, prm, s) : launch_bwd<64, false, true>(tq, tk, tv, tdo, tdq, prm, s);
-  } else {
-    if (D == 128) rc = bf16 ? launch_bwd<128, true, false>(tq, tk, tv, tdo, tdq, prm, s) : launch_bwd<128, false, false>(tq, tk, tv, tdo, tdq, prm, s);
-    else rc = bf16 ? launch_bwd<64, true, false>(tq, tk, tv, tdo, tdq, prm, s) : launch_bwd<64, false, false>(tq, tk, tv, tdo, tdq, prm, s);
+  const int mode = ext ? ((prm.ex.bias != nullptr ? 1 : 0) | (prm.ex.dropout ? 2 : 0)) : 0;
+#define FO_BWD_MODE(M)                                                                                     \
+  case M:                                                                                                  \
+    if (D == 128) rc = bf16 ? launch_bwd<128, true, M>(tq, tk, tv, tdo, tdq, prm, s) : launch_bwd<128, false, M>(tq, tk, tv, tdo, tdq, prm, s); \
+    else rc = bf16 ? launch_bwd<64, true, M>(tq, tk, tv, tdo, tdq, prm, s) : launch_bwd<64, false, M>(tq, tk, tv, tdo, tdq, prm, s);            \
+    break;
+  switch (mode) {
+    FO_BWD_MODE(0)
+    FO_BWD_MODE(1)
+    FO_BWD_MODE(2)
+    default:
+    FO_BWD_MODE(3)
   }
+#undef FO_BWD_MODE
   if (rc) return rc;
 
   {

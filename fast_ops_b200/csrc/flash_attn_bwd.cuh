@@ -64,7 +64,9 @@ struct BwdConfig {
   static constexpr int kOffBars = kOffDS + kPBytes;
   static constexpr int kNumBars = 7;
   static constexpr int kOffMisc = kOffBars + kNumBars * 8;
-  static constexpr int kSmemBytes = kOffMisc + 64 + 1024;
+  // [128] float: a row-independent bias of this key tile; read as float4, so 16-byte aligned
+  static constexpr int kOffBias = (kOffMisc + 64 + 15) & ~15;
+  static constexpr int kSmemBytes = kOffBias + 128 * 4 + 1024;
   static constexpr uint32_t kTmemCols = 512;
   static constexpr uint32_t kColDK = 0, kColDV = D, kColS = 256, kColDP = 384;  // dQ reuses kColS
 };
@@ -78,7 +80,9 @@ __device__ __forceinline__ void store_swizzled_unit(uint8_t* tile, int r, int u,
 }
 
 // grid = (key tiles, B*H); block = 320.
-template <int D, bool kBf16, bool kExt>
+static_assert(BwdConfig<128>::kOffBias % 16 == 0 && BwdConfig<64>::kOffBias % 16 == 0, "float4 reads");
+
+template <int D, bool kBf16, int kExt>
 __global__ void __launch_bounds__(320, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
@@ -157,10 +161,24 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tS = tmem_base + Cfg::kColS + lane_base;
     const uint32_t tDP = tmem_base + Cfg::kColDP + lane_base;
-    const bool has_bias = kExt && prm.ex.bias != nullptr;
-    const bool has_drop = kExt && prm.ex.dropout;
+    constexpr bool has_bias = (kExt & 1) != 0;
+    constexpr bool has_drop = (kExt & 2) != 0;
     // with dropout dP arrives without the 1 / (1 - p) factor of the kept elements
     const float dp_scale = kExt ? prm.scale * prm.ex.drop_rescale : prm.scale;
+    // A bias that is the same for every query row is the same for every query tile of this CTA
+    // (its key tile is fixed): fetched once into shared memory.
+    const bool vec_bias = has_bias && prm.ex.bias_stride_q == 0;
+    float* sb = reinterpret_cast<float*>(smem + Cfg::kOffBias);
+    if constexpr (kExt) {
+      if (vec_bias) {
+        if (tid < kBlockN) {
+          const uint8_t* base = static_cast<const uint8_t*>(prm.ex.bias) +
+                                (b * prm.ex.bias_stride_b + h * prm.ex.bias_stride_h) * (prm.ex.bias_f32 ? 4 : 2);
+          sb[tid] = (k0 + tid < prm.Sk) ? load_bias1<kBf16>(prm.ex, base, k0 + tid) : 0.f;
+        }
+        named_barrier_sync(1, 256);
+      }
+    }
     for (int it = 0; it < n_iter; ++it) {
       const int i = i0 + it;
       const int q0 = i * kBlockM;
@@ -182,6 +200,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       const float delta = row_ok ? prm.delta[static_cast<int64_t>(bh) * prm.Sq + row] : 0.f;
       const bool need_mask = (k0 + kBlockN > prm.Sk) || (prm.causal && k0 + kBlockN - 1 > q0);
+      if constexpr (kExt) {
+        // matrix bias: ask for this thread's 64 columns of the next query tile's row now
+        if (has_bias && !vec_bias && it + 1 < n_iter && row + kBlockM < prm.Sq) {
+          const int c0 = k0 + half * 64;
+          if (c0 < prm.Sk)
+            prefetch_bias(prm.ex, bias_row + static_cast<int64_t>(kBlockM) * prm.ex.bias_stride_q * (prm.ex.bias_f32 ? 4 : 2),
+                          c0, min(64, prm.Sk - c0));
+        }
+      }
       mbar_wait(bar_s_full, it & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_MMA);
       tcgen05_fence_after_sync();
       if (warp == 0) bwd_trace(prm, 0, it, 0);
@@ -195,21 +222,34 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         uint32_t sr[32], dpr[32];
         tmem_ld32(tS + c * 32, sr);
         tmem_ld32(tDP + c * 32, dpr);
-        float bb[kExt ? 32 : 1];
+        float bb[kExt ? 32 : 1];  // matrix bias only: fetched while the tensor-memory loads fly
         if constexpr (kExt) {
-          if (has_bias) load_bias32<kBf16>(prm.ex, bias_row, k0 + c * 32, prm.Sk, bb);
+          if (has_bias && !vec_bias) load_bias32<kBf16>(prm.ex, bias_row, k0 + c * 32, prm.Sk, bb);
         }
         tmem_ld_wait(sr);
         tmem_ld_wait(dpr);
         // P in place over the S registers; the mask (rare: diagonal and ragged tiles) is a
         // separate, warp-uniform branch so that full tiles pay nothing for it
-        if (has_bias) {
-          if constexpr (kExt) {
+        bool plain = true;
+        if constexpr (kExt) {
+          if (vec_bias) {
+            plain = false;
+#pragma unroll
+            for (int x = 0; x < 32; x += 4) {
+              const float4 t = *reinterpret_cast<const float4*>(sb + c * 32 + x);  // broadcast read
+              sr[x + 0] = __float_as_uint(fast_exp2(fmaf(__uint_as_float(sr[x + 0]), prm.scale_log2, t.x) - lse2));
+              sr[x + 1] = __float_as_uint(fast_exp2(fmaf(__uint_as_float(sr[x + 1]), prm.scale_log2, t.y) - lse2));
+              sr[x + 2] = __float_as_uint(fast_exp2(fmaf(__uint_as_float(sr[x + 2]), prm.scale_log2, t.z) - lse2));
+              sr[x + 3] = __float_as_uint(fast_exp2(fmaf(__uint_as_float(sr[x + 3]), prm.scale_log2, t.w) - lse2));
+            }
+          } else if (has_bias) {
+            plain = false;
 #pragma unroll
             for (int x = 0; x < 32; ++x)
               sr[x] = __float_as_uint(fast_exp2(fmaf(__uint_as_float(sr[x]), prm.scale_log2, bb[x]) - lse2));
           }
-        } else {
+        }
+        if (plain) {
 #pragma unroll
           for (int x = 0; x < 32; ++x)
             sr[x] = __float_as_uint(fast_exp2(fmaf(__uint_as_float(sr[x]), prm.scale_log2, -lse2)));

@@ -101,6 +101,24 @@ struct AttnParams {
   AttnExtras ex;  // read only by the kernel variants built for bias / dropout
 };
 
+// One element of a bias row as log2(e) * value; `base` points at column 0 of the row.
+template <bool kBf16>
+__device__ __forceinline__ float load_bias1(const AttnExtras& ex, const uint8_t* base, int col) {
+  constexpr float kLog2e = 1.4426950408889634f;
+  if (ex.bias_f32) return __ldg(reinterpret_cast<const float*>(base) + col) * kLog2e;
+  const uint16_t h = __ldg(reinterpret_cast<const uint16_t*>(base) + col);
+  if constexpr (kBf16) return __uint_as_float(static_cast<uint32_t>(h) << 16) * kLog2e;
+  else return __half2float(__ushort_as_half(h)) * kLog2e;
+}
+
+// L2 prefetch of the `ncols` bias elements of a row starting at column col0 (row pointer non-null,
+// columns clamped to Sk by the caller).
+__device__ __forceinline__ void prefetch_bias(const AttnExtras& ex, const uint8_t* rowp, int col0, int ncols) {
+  const int esize = ex.bias_f32 ? 4 : 2;
+  const uint8_t* p = rowp + static_cast<int64_t>(col0) * esize;
+  for (int off = 0; off < ncols * esize; off += 128) prefetch_l2(p + off);
+}
+
 constexpr int kTraceRoles = 3;   // softmax tile 0, softmax tile 1, MMA issuer
 constexpr int kTraceIters = 160;
 constexpr int kTraceEvents = 6;

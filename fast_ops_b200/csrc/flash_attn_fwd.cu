@@ -267,12 +267,20 @@ static int attn_fwd_impl(const void* q, const void* k, const void* v, void* o, f
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool bf16 = dtype == FO_BF16;
   if (ext) {  // bias and dropout exist in the warp-specialised kernel only
-    if (D == 128) return bf16 ? fo::launch_ws<128, true, true>(tq, tk, tv, prm, s) : fo::launch_ws<128, false, true>(tq, tk, tv, prm, s);
-    return bf16 ? fo::launch_ws<64, true, true>(tq, tk, tv, prm, s) : fo::launch_ws<64, false, true>(tq, tk, tv, prm, s);
+    const int mode = (prm.ex.bias != nullptr ? 1 : 0) | (prm.ex.dropout ? 2 : 0);
+#define FO_WS_EXT(M)                                                                                           \
+  if (mode == M) {                                                                                             \
+    if (D == 128) return bf16 ? fo::launch_ws<128, true, M>(tq, tk, tv, prm, s) : fo::launch_ws<128, false, M>(tq, tk, tv, prm, s); \
+    return bf16 ? fo::launch_ws<64, true, M>(tq, tk, tv, prm, s) : fo::launch_ws<64, false, M>(tq, tk, tv, prm, s);                 \
+  }
+    FO_WS_EXT(1)
+    FO_WS_EXT(2)
+    FO_WS_EXT(3)
+#undef FO_WS_EXT
   }
   if (chosen_impl() == AttnImpl::kWarpSpecialized) {
-    if (D == 128) return bf16 ? fo::launch_ws<128, true, false>(tq, tk, tv, prm, s) : fo::launch_ws<128, false, false>(tq, tk, tv, prm, s);
-    return bf16 ? fo::launch_ws<64, true, false>(tq, tk, tv, prm, s) : fo::launch_ws<64, false, false>(tq, tk, tv, prm, s);
+    if (D == 128) return bf16 ? fo::launch_ws<128, true, 0>(tq, tk, tv, prm, s) : fo::launch_ws<128, false, 0>(tq, tk, tv, prm, s);
+    return bf16 ? fo::launch_ws<64, true, 0>(tq, tk, tv, prm, s) : fo::launch_ws<64, false, 0>(tq, tk, tv, prm, s);
   }
   if (D == 128) return bf16 ? launch_simple<128, true>(tq, tk, tv, prm, s) : launch_simple<128, false>(tq, tk, tv, prm, s);
   return bf16 ? launch_simple<64, true>(tq, tk, tv, prm, s) : launch_simple<64, false>(tq, tk, tv, prm, s);

@@ -37,13 +37,16 @@ struct WsConfig {
   static constexpr int kOffKV = 2 * kTileBytes;
   static constexpr int kOffAlpha = kOffKV + kStages * kTileBytes;  // [2 tiles][2 buffers][128] float
   static constexpr int kOffFinal = kOffAlpha + 2 * 2 * 128 * 4;    // [2 tiles][l, m][128] float
-  static constexpr int kOffBars = kOffFinal + 2 * 2 * 128 * 4;
+  static constexpr int kOffBias = kOffFinal + 2 * 2 * 128 * 4;     // [2 tiles][2 buffers][128] float
+  static constexpr int kOffBars = kOffBias + 2 * 2 * 128 * 4;
   static constexpr int kNumBars = 1 + 2 * kStages + 2 * 6;
   static constexpr int kOffMisc = kOffBars + kNumBars * 8;
   static constexpr int kSmemBytes = kOffMisc + 64 + 1024 /* alignment slack */;
   static constexpr uint32_t kTmemCols = 512;
   static constexpr uint32_t kColS0 = 0, kColO0 = 256;
 };
+
+static_assert(WsConfig<128>::kOffBias % 16 == 0 && WsConfig<64>::kOffBias % 16 == 0, "float4 reads");
 
 // A row keeps its reference maximum until the true maximum exceeds it by this much (log2
 // units): exp2 arguments then stay below 8, P stays below 256, and most key tiles need no
@@ -62,9 +65,11 @@ template <int kRegs> __device__ __forceinline__ void reg_dealloc() {
 // grid = (num_q_pairs * B * H); block = 512.  Consecutive blocks sweep a group of heads whose K
 // and V fit in L2 together, so the query tiles of those heads re-read K/V from L2 rather than
 // from HBM; within the group the pairs with the most key tiles (causal mask) start first.
-// kExt builds the variant with the optional additive bias and dropout (prm.ex); the plain
-// variant contains none of that code.
-template <int D, bool kBf16, bool kExt>
+// kExt selects what is compiled in besides plain attention: bit 0 the additive bias, bit 1
+// dropout (both described by prm.ex).  They are compile-time choices because a uniform run-time
+// test inside the unrolled loops gets if-converted, and the unused path then still costs issue
+// slots.
+template <int D, bool kBf16, int kExt>
 __global__ void __launch_bounds__(512, 1)
 attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                    const __grid_constant__ CUtensorMap tm_v, const AttnParams prm) {
@@ -79,6 +84,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   uint8_t* sKV = smem + Cfg::kOffKV;  // kStages tiles
   float* s_alpha = reinterpret_cast<float*>(smem + Cfg::kOffAlpha);
   float* s_final = reinterpret_cast<float*>(smem + Cfg::kOffFinal);
+  float* s_bias = reinterpret_cast<float*>(smem + Cfg::kOffBias);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kOffBars);
   uint64_t* bar_q_full = bars;                  // TMA -> MMA
   uint64_t* bar_kv_full = bars + 1;             // [kStages] TMA -> MMA
@@ -165,8 +171,8 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     float m_run = -INFINITY, l_run = 0.f;
     // bias row of this thread (null: no bias, or a row past the end) and the dropout index of
     // its column 0; with a bias the scores are scaled when the bias is added, not in the exponent
-    const bool has_bias = kExt && prm.ex.bias != nullptr;
-    const bool has_drop = kExt && prm.ex.dropout;
+    constexpr bool has_bias = (kExt & 1) != 0;
+    constexpr bool has_drop = (kExt & 2) != 0;
     const uint8_t* bias_row = nullptr;
     uint32_t drop_row = 0;
     if constexpr (kExt) {
@@ -178,9 +184,35 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                  static_cast<uint32_t>(row) * static_cast<uint32_t>(prm.Sk);
     }
     const float exp_scale = has_bias ? 1.f : prm.scale_log2;
+    // A bias that is the same for every query row ("vector") is staged through shared memory,
+    // one key tile ahead: thread r fetches column r of the next tile while this tile is computed.
+    const bool vec_bias = has_bias && prm.ex.bias_stride_q == 0;
+    const uint8_t* bias_vec = nullptr;
+    float* sb = s_bias + s * 256;
+    float bias_next = 0.f;
+    if constexpr (kExt) {
+      if (vec_bias) {
+        bias_vec = static_cast<const uint8_t*>(prm.ex.bias) +
+                   (b * prm.ex.bias_stride_b + h * prm.ex.bias_stride_h) * (prm.ex.bias_f32 ? 4 : 2);
+        bias_next = (r < prm.Sk) ? load_bias1<kBf16>(prm.ex, bias_vec, r) : 0.f;
+      }
+    }
 
     for (int j = 0; j < n_s; ++j) {
       const int k0 = j * kBlockN;
+      if constexpr (kExt) {
+        if (vec_bias) {
+          sb[(j & 1) * 128 + r] = bias_next;
+          const int col = k0 + kBlockN + r;
+          bias_next = (j + 1 < n_s && col < prm.Sk) ? load_bias1<kBf16>(prm.ex, bias_vec, col) : 0.f;
+          // the 128 threads of this tile; a buffer is rewritten two tiles later, behind the
+          // barrier of the tile in between
+          named_barrier_sync(1 + s, 128);
+        } else if (bias_row != nullptr && j + 1 < n_s) {
+          const int c0 = k0 + kBlockN;
+          prefetch_bias(prm.ex, bias_row, c0, min(kBlockN, prm.Sk - c0));
+        }
+      }
       mbar_wait(bar_s_full + s, j & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_MMA);
       tcgen05_fence_after_sync();
       if ((warp & 3) == 0) trace_event(prm, s, j, 0);
@@ -205,7 +237,17 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         if (c + 1 < 4) tmem_ld32(tS + (c + 1) * 32, sr[c + 1]);
 #endif
         if constexpr (kExt) {
-          if (has_bias) {
+          if (vec_bias) {
+            const float4* bv = reinterpret_cast<const float4*>(sb + (j & 1) * 128 + c * 32);
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              const float4 t = bv[i >> 2];  // the same address in every thread: a broadcast
+              sr[c][i + 0] = __float_as_uint(fmaf(__uint_as_float(sr[c][i + 0]), prm.scale_log2, t.x));
+              sr[c][i + 1] = __float_as_uint(fmaf(__uint_as_float(sr[c][i + 1]), prm.scale_log2, t.y));
+              sr[c][i + 2] = __float_as_uint(fmaf(__uint_as_float(sr[c][i + 2]), prm.scale_log2, t.z));
+              sr[c][i + 3] = __float_as_uint(fmaf(__uint_as_float(sr[c][i + 3]), prm.scale_log2, t.w));
+            }
+          } else if (has_bias) {
             float bb[32];
             load_bias32<kBf16>(prm.ex, bias_row, k0 + c * 32, prm.Sk, bb);
 #pragma unroll
@@ -470,7 +512,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   if (warp == 12) tmem_dealloc(tmem_base, Cfg::kTmemCols);
 }
 
-template <int D, bool kBf16, bool kExt>
+template <int D, bool kBf16, int kExt>
 int launch_ws(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& prm,
               cudaStream_t stream) {
   auto kernel = attn_fwd_ws_kernel<D, kBf16, kExt>;

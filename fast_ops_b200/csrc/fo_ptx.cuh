@@ -121,6 +121,12 @@ __device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* map, const 
       : "memory");
 }
 
+// Asks for the 128-byte line holding `p` to be brought into L2 (a hint: no fault on a bad address
+// is specified, so callers pass addresses inside their tensors only).
+__device__ __forceinline__ void prefetch_l2(const void* p) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
+
 // bar.sync on a named barrier (id 1..15) among `count` threads of the CTA
 __device__ __forceinline__ void named_barrier_sync(int id, int count) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
