@@ -288,6 +288,32 @@ def bench_attention_bwd(d: Dist, name: str, steps: int, warmup: int, peaks):
                          "peak_source": peaks["source"] + " cuBLAS bf16 burst"}}
 
 
+def bench_attention_variants(d: Dist, name: str, steps: int, warmup: int, peaks):
+    """Forward and backward of the same shape with a per-head key bias (ALiBi-like, fp32, shape
+    (1, H, 1, S)) and with dropout p = 0.17: TFLOP/s per GPU, the plain kernels' FLOP count."""
+    import fast_ops_b200._lib as L
+    from fast_ops_b200.flash_attention import flash_attention_backward, flash_attention_forward
+
+    B, H, S, D, causal = ATTN[name]
+    q, k, v = attn_inputs(B, H, S, D, d.device, seed=4000 + d.rank)
+    dout = attn_inputs(B, H, S, D, d.device, seed=5000 + d.rank)[0]
+    gen = torch.Generator(device=d.device).manual_seed(6000 + d.rank)
+    bias = torch.randn(1, H, 1, S, generator=gen, device=d.device, dtype=torch.float32)
+    flops = attn_flops(B, H, S, D, causal)
+    out = {"workload": f"{name} with bias (1,H,1,S) fp32 / dropout 0.17: B={B} H={H} S={S} D={D} bf16 causal={causal}",
+           "unit": "TFLOP/s per GPU"}
+    for label, kw in (("bias", {"bias": bias}), ("dropout", {"dropout_p": 0.17, "rng": (0, 0)})):
+        ms_f, _ = timed_steps(d, lambda: flash_attention_forward(q, k, v, causal=causal, **kw), steps, warmup)
+        o, lse = flash_attention_forward(q, k, v, causal=causal, return_lse=True, **kw)
+        ms_b, _ = timed_steps(d, lambda: flash_attention_backward(dout, q, k, v, o, lse, causal=causal, **kw),
+                              steps, warmup)
+        out[label] = {"fwd": flops / (ms_f * 1e-3) / 1e12, "fwd_ms": ms_f,
+                      "bwd": 2.5 * flops / (ms_b * 1e-3) / 1e12, "bwd_ms": ms_b}
+    if L.device_status(d.local_rank) != 0:
+        raise RuntimeError("an attention kernel reported a timed-out wait")
+    return out
+
+
 def cpu_attention_sample(name: str, row_stride: int, reps: int):
     """Times the CPU oracle on one (batch, head) slice of the workload, every `row_stride`-th
     query row (the causal row costs are sampled evenly), all host threads."""
@@ -554,6 +580,7 @@ def main():
             also["attn_c2"]["unit"] = "TFLOP/s"
         if not args.workload.startswith("attn_bwd"):
             also["attn_bwd_c3"] = bench_attention_bwd(d, "attn_c3", max(3, args.steps // 4), 2, peaks)
+            also["attn_bias_dropout_c3"] = bench_attention_variants(d, "attn_c3", max(3, args.steps // 4), 2, peaks)
         if args.workload != "lion_c4":
             also["lion_c4"] = bench_lion_c4(d, args.steps, args.warmup, peaks)
         if args.workload != "lion_c5":
