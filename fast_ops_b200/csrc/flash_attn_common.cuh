@@ -99,6 +99,7 @@ struct AttnParams {
   // Optional timeline of CTA 0 (debug): [role][key tile][event] SM clock values, or null.
   unsigned long long* trace;
   AttnExtras ex;  // read only by the kernel variants built for bias / dropout
+  int ping_pong;  // 64-key-step kernel: the two query tiles take turns on the ex2 units (1) or not (0)
 };
 
 // One element of a bias row as log2(e) * value; `base` points at column 0 of the row.

@@ -11,6 +11,7 @@
 
 #include "flash_attn_simple.cuh"
 #include "flash_attn_ws.cuh"
+#include "flash_attn_ws64.cuh"
 #include "fo_host.h"
 #include "fo_tma.h"
 
@@ -133,13 +134,16 @@ int set_smem(Kernel kernel, int bytes) {
 }
 
 
-enum class AttnImpl { kSimple, kWarpSpecialized };
+enum class AttnImpl { kAuto, kSimple, kWarpSpecialized, kWarpSpecialized64 };
 
-// FO_ATTN_IMPL=simple|ws selects the kernel (default: the warp-specialised one).
+// FO_ATTN_IMPL=simple|ws|ws64 forces a kernel: the bring-up kernel, the warp-specialised one with
+// 128-key softmax tiles, or the one with 64-key steps.  Unset: chosen per call (below).
 AttnImpl chosen_impl() {
   const char* e = std::getenv("FO_ATTN_IMPL");
   if (e && std::strcmp(e, "simple") == 0) return AttnImpl::kSimple;
-  return AttnImpl::kWarpSpecialized;
+  if (e && std::strcmp(e, "ws64") == 0) return AttnImpl::kWarpSpecialized64;
+  if (e && std::strcmp(e, "ws") == 0) return AttnImpl::kWarpSpecialized;
+  return AttnImpl::kAuto;
 }
 
 template <int D, bool kBf16>
@@ -248,6 +252,10 @@ static int attn_fwd_impl(const void* q, const void* k, const void* v, void* o, f
   prm.num_q_tiles = (Sq + kBlockM - 1) / kBlockM;
   prm.trace = g_attn_trace;
   prm.kv_head_bcast = kv_bcast ? 1 : 0;
+  {
+    const char* e = std::getenv("FO_ATTN_PINGPONG");
+    prm.ping_pong = (e && std::atoi(e) == 0) ? 0 : 1;
+  }
   std::memset(&prm.ex, 0, sizeof(prm.ex));
   prm.ex.drop_rescale = 1.f;
   const bool ext = ex != nullptr && (ex->bias != nullptr || ex->dropout);
@@ -266,22 +274,37 @@ static int attn_fwd_impl(const void* q, const void* k, const void* v, void* o, f
 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool bf16 = dtype == FO_BF16;
-  if (ext) {  // bias and dropout exist in the warp-specialised kernel only
-    const int mode = (prm.ex.bias != nullptr ? 1 : 0) | (prm.ex.dropout ? 2 : 0);
-#define FO_WS_EXT(M)                                                                                           \
-  if (mode == M) {                                                                                             \
-    if (D == 128) return bf16 ? fo::launch_ws<128, true, M>(tq, tk, tv, prm, s) : fo::launch_ws<128, false, M>(tq, tk, tv, prm, s); \
-    return bf16 ? fo::launch_ws<64, true, M>(tq, tk, tv, prm, s) : fo::launch_ws<64, false, M>(tq, tk, tv, prm, s);                 \
+  AttnImpl impl = chosen_impl();
+  if (impl == AttnImpl::kAuto) {
+    // The 64-key-step kernel fills and drains its pipeline faster (S is double-buffered, one MMA
+    // issuer per query tile) and wins while a CTA sees few key tiles; in a long steady state the
+    // 128-key kernel's fewer, larger steps win.  Measured crossover: about 24 key tiles per CTA on
+    // average (causal S = 8192 is a tie; causal S <= 4096 gains 7-35 %).
+    const int n_kv = (Sk + kBlockN - 1) / kBlockN;
+    const int avg_tiles = causal ? (n_kv + 1) / 2 : n_kv;
+    // With a bias or dropout the 64-key kernel is as fast or faster at every length measured.
+    impl = (ext || avg_tiles <= 24) ? AttnImpl::kWarpSpecialized64 : AttnImpl::kWarpSpecialized;
   }
-    FO_WS_EXT(1)
-    FO_WS_EXT(2)
-    FO_WS_EXT(3)
-#undef FO_WS_EXT
+  const int mode = ext ? ((prm.ex.bias != nullptr ? 1 : 0) | (prm.ex.dropout ? 2 : 0)) : 0;
+  // bias and dropout exist in the warp-specialised kernels only
+#define FO_WS_MODE(LAUNCH, M)                                                                          \
+  if (mode == M) {                                                                                     \
+    if (D == 128) return bf16 ? fo::LAUNCH<128, true, M>(tq, tk, tv, prm, s) : fo::LAUNCH<128, false, M>(tq, tk, tv, prm, s); \
+    return bf16 ? fo::LAUNCH<64, true, M>(tq, tk, tv, prm, s) : fo::LAUNCH<64, false, M>(tq, tk, tv, prm, s);                 \
   }
-  if (chosen_impl() == AttnImpl::kWarpSpecialized) {
-    if (D == 128) return bf16 ? fo::launch_ws<128, true, 0>(tq, tk, tv, prm, s) : fo::launch_ws<128, false, 0>(tq, tk, tv, prm, s);
-    return bf16 ? fo::launch_ws<64, true, 0>(tq, tk, tv, prm, s) : fo::launch_ws<64, false, 0>(tq, tk, tv, prm, s);
+  if (impl == AttnImpl::kWarpSpecialized64) {
+    FO_WS_MODE(launch_ws64, 0)
+    FO_WS_MODE(launch_ws64, 1)
+    FO_WS_MODE(launch_ws64, 2)
+    FO_WS_MODE(launch_ws64, 3)
   }
+  if (impl != AttnImpl::kSimple || mode != 0) {
+    FO_WS_MODE(launch_ws, 0)
+    FO_WS_MODE(launch_ws, 1)
+    FO_WS_MODE(launch_ws, 2)
+    FO_WS_MODE(launch_ws, 3)
+  }
+#undef FO_WS_MODE
   if (D == 128) return bf16 ? launch_simple<128, true>(tq, tk, tv, prm, s) : launch_simple<128, false>(tq, tk, tv, prm, s);
   return bf16 ? launch_simple<64, true>(tq, tk, tv, prm, s) : launch_simple<64, false>(tq, tk, tv, prm, s);
 }

@@ -1,0 +1,571 @@
+// Attention forward, warp-specialised kernel for sm_100a with 64-key softmax steps.
+//
+// Same roles, shared-memory ring and tensor-memory budget as the kernel in flash_attn_ws.cuh
+// (one CTA = two consecutive 128-row query tiles of one (batch, head); warps 0-3 / 4-7 softmax,
+// 8-11 correction and epilogue, 12 and 14 MMA issuers (one per query tile), 13 TMA producer), but
+// the 128 score columns that
+// a query tile owns in tensor memory are used as TWO buffers of 64 key columns:
+// (the kernel in flash_attn_ws.cuh has a single MMA issuer and leaves warps 14-15 idle)
+//
+//   tensor memory: S0a | S0b | S1a | S1b | O0 | O1      (64 + 64 + 64 + 64 + D + D columns)
+//
+// A key tile of 128 rows in shared memory is consumed as two steps of 64 keys.  While the
+// softmax threads of a query tile work on step t (buffer t & 1), the tensor core already holds
+// or is computing S of step t + 1 in the other buffer, so the threads go from one step to the
+// next without waiting for an MMA: the chain "P written -> P V -> next Q K^T -> S ready", which
+// bounds the 128-column kernel, is off their critical path.  P of a step overwrites the first
+// 32 columns of its own buffer and is read by the P V MMA of that step, after which the buffer
+// takes the Q K^T of step t + 2.
+#pragma once
+
+#include "flash_attn_common.cuh"
+#include "flash_attn_ws.cuh"
+#include "fo_host.h"
+
+namespace fo {
+
+constexpr int kStepN = 64;  // keys per softmax step
+
+template <int D>
+struct Ws64Config : WsConfig<D> {
+  // barriers: q_full, kv_full/empty per stage, then s_full[2][2], p_full[2][2], o_full[2],
+  // corr[2][2], final[2], o_done[2]
+  static constexpr int kNumBars = 1 + 2 * WsConfig<D>::kStages + 4 + 4 + 2 + 4 + 2 + 2;
+  static constexpr int kOffMisc = WsConfig<D>::kOffBars + kNumBars * 8;
+  static constexpr int kSmemBytes = kOffMisc + 64 + 1024 /* alignment slack */;
+};
+
+template <int D, bool kBf16, int kExt>
+__global__ void __launch_bounds__(512, 1)
+attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                     const __grid_constant__ CUtensorMap tm_v, const AttnParams prm) {
+  using Cfg = Ws64Config<D>;
+  constexpr int kTileBytes = Cfg::kTileBytes;
+  constexpr int kStages = Cfg::kStages;
+  constexpr int kBoxes = Cfg::kBoxes;
+
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint8_t* sQ = smem + Cfg::kOffQ;    // two tiles
+  uint8_t* sKV = smem + Cfg::kOffKV;  // kStages tiles
+  float* s_alpha = reinterpret_cast<float*>(smem + Cfg::kOffAlpha);
+  float* s_final = reinterpret_cast<float*>(smem + Cfg::kOffFinal);
+  float* s_bias = reinterpret_cast<float*>(smem + Cfg::kOffBias);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kOffBars);
+  uint64_t* bar_q_full = bars;                     // TMA -> MMA
+  uint64_t* bar_kv_full = bars + 1;                // [kStages] TMA -> MMA
+  uint64_t* bar_kv_empty = bar_kv_full + kStages;  // [kStages] MMA -> TMA
+  uint64_t* bar_s_full = bar_kv_empty + kStages;   // [2 tiles][2 buffers] MMA -> softmax
+  // [2][2] softmax and correction -> MMA (256 arrivals): P of the step is in tensor memory (128
+  // softmax threads) and O has been rescaled if the step needed it (128 correction threads).
+  // One barrier for both, because every wait on the issuing warp's path costs about 200 cycles
+  // even when the phase completed long ago.  The correction threads arrive as soon as they have
+  // the step's rescale factors, unless a factor differs from 1: only then do they wait for the
+  // previous P V and rescale O first.
+  uint64_t* bar_p_full = bar_s_full + 4;
+  uint64_t* bar_o_full = bar_p_full + 4;           // [2] MMA -> correction
+  // [2][2] softmax -> correction (128 arrivals), one barrier per step parity: the softmax
+  // threads can be two steps ahead of the correction warps, which a single barrier's phase
+  // bit could not tell from zero steps ahead
+  uint64_t* bar_corr = bar_o_full + 2;
+  uint64_t* bar_final = bar_corr + 4;              // [2] softmax -> correction, once
+  // [2] MMA -> epilogue, once: every P V of the tile has finished.  bar_o_full cannot serve: by
+  // then nobody may have waited on it for many steps, and its phase bit alone does not say
+  // whether the last P V is the one that completed.
+  uint64_t* bar_o_done = bar_final + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::kOffMisc);
+  volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* skip = cta_abort + 1;
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int bh_count = prm.B * prm.H;
+  const int num_pairs = (prm.num_q_tiles + 1) >> 1;
+  // block -> (head group, pair, head): see flash_attn_ws.cuh
+  const int group_blocks = prm.head_group * num_pairs;
+  const int group = static_cast<int>(blockIdx.x) / group_blocks;
+  const int in_group = static_cast<int>(blockIdx.x) - group * group_blocks;
+  const int heads_here = min(prm.head_group, bh_count - group * prm.head_group);
+  const int pair = num_pairs - 1 - in_group / heads_here;
+  const int bh = group * prm.head_group + in_group % heads_here;
+  const int b = bh / prm.H;
+  const int h = bh - b * prm.H;
+  const int hk = prm.kv_head_bcast ? 0 : h;  // head coordinate of K and V
+  // keys visible to query tile 0 / 1 of this pair, in 64-key steps (T) and 128-key tiles (n)
+  const int vis0 = prm.causal ? min(prm.Sk, (2 * pair + 1) * kBlockM) : prm.Sk;
+  const int vis1 = prm.causal ? min(prm.Sk, (2 * pair + 2) * kBlockM) : prm.Sk;
+  const int T0 = (vis0 + kStepN - 1) / kStepN;  // T1 >= T0 >= 1
+  const int T1 = (vis1 + kStepN - 1) / kStepN;
+  const int n1 = (T1 + 1) >> 1;
+
+  if (tid == 0) {
+    *cta_abort = 0;
+    *skip = *reinterpret_cast<volatile int*>(prm.device_status);
+    mbar_init(bar_q_full, 1);
+    for (int i = 0; i < kStages; ++i) {
+      mbar_init(bar_kv_full + i, 1);
+      mbar_init(bar_kv_empty + i, 2);  // one arrival from each MMA-issuing warp
+    }
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(bar_s_full + i, 1);
+      mbar_init(bar_p_full + i, 256);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar_o_full + s, 1);
+      mbar_init(bar_corr + 2 * s, 128);
+      mbar_init(bar_corr + 2 * s + 1, 128);
+      mbar_init(bar_final + s, 128);
+      mbar_init(bar_o_done + s, 1);
+    }
+    fence_mbar_init();
+    prefetch_tensormap(&tm_q);
+    prefetch_tensormap(&tm_k);
+    prefetch_tensormap(&tm_v);
+  }
+  __syncthreads();
+  if (*skip) return;  // another CTA already timed out: do nothing
+
+  if (warp == 12) {
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish_alloc_permit();
+  }
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  tcgen05_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  int* const dstat = prm.device_status;
+
+  if (warp < 8) {
+    // ================================ softmax ================================
+    reg_alloc<192>();
+    const int s = warp >> 2;
+    const int r = (warp & 3) * 32 + lane;
+    const int q0 = (2 * pair + s) * kBlockM;
+    const int row = q0 + r;
+    const int T_s = s ? T1 : T0;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t tS_tile = tmem_base + Cfg::kColS0 + s * kBlockN + lane_base;
+    float* alpha_slot = s_alpha + s * 256 + r;
+    float m_run = -INFINITY, l_run = 0.f;
+    constexpr bool has_bias = (kExt & 1) != 0;
+    constexpr bool has_drop = (kExt & 2) != 0;
+    const uint8_t* bias_row = nullptr;
+    uint32_t drop_row = 0;
+    if constexpr (kExt != 0) {
+      if (has_bias && row < prm.Sq)
+        bias_row = static_cast<const uint8_t*>(prm.ex.bias) +
+                   (b * prm.ex.bias_stride_b + h * prm.ex.bias_stride_h + static_cast<int64_t>(row) * prm.ex.bias_stride_q) *
+                       (prm.ex.bias_f32 ? 4 : 2);
+      drop_row = prm.ex.drop_base + static_cast<uint32_t>(bh) * static_cast<uint32_t>(prm.Sq) * static_cast<uint32_t>(prm.Sk) +
+                 static_cast<uint32_t>(row) * static_cast<uint32_t>(prm.Sk);
+    }
+    // with a bias the scores are scaled when the bias is added, not in the exponent
+    const float exp_scale = has_bias ? 1.f : prm.scale_log2;
+    // a row-independent bias goes through shared memory, fetched one 128-key tile ahead
+    const bool vec_bias = has_bias && prm.ex.bias_stride_q == 0;
+    const uint8_t* bias_vec = nullptr;
+    float* sb = s_bias + s * 256;
+    float bias_next = 0.f;
+    if constexpr (kExt != 0) {
+      if (vec_bias) {
+        bias_vec = static_cast<const uint8_t*>(prm.ex.bias) +
+                   (b * prm.ex.bias_stride_b + h * prm.ex.bias_stride_h) * (prm.ex.bias_f32 ? 4 : 2);
+        bias_next = (r < prm.Sk) ? load_bias1<kBf16>(prm.ex, bias_vec, r) : 0.f;
+      }
+    }
+
+    // S of the next step is normally complete long before it is needed: polled once while the
+    // current step's exponentials are in flight, waited on only if that poll failed
+    // The two tiles' softmax warps share the ex2 units.  Left alone they fall into lockstep: both
+    // reduce maxima at the same time (ex2 idle), then both exponentiate (ex2 contended).  The
+    // exponentials of the two tiles are therefore made to alternate with a pair of named barriers
+    // (tile 0 goes first): while one tile exponentiates, the other loads S, reduces its maxima
+    // and stores P.  A tile that runs out of steps keeps passing the turn on.
+    constexpr int kTurn0 = 3, kTurn1 = 4;  // named barriers: "tile 0 may exponentiate", "tile 1 may"
+    const bool ping_pong = prm.ping_pong != 0;
+    if (ping_pong && s == 1) named_barrier_arrive(kTurn0, 256);
+
+    uint32_t sr[2][32];  // scores of the current step (scaled and biased already when there is a bias)
+    float mx = -INFINITY;  // their row maximum
+
+    // Stages the row-independent bias of the key tile that step `tn` (even) starts.
+    auto stage_vec_bias = [&](int tn) {
+      const int j = tn >> 1;
+      sb[(j & 1) * 128 + r] = bias_next;
+      const int col = tn * kStepN + kBlockN + r;
+      bias_next = (col < prm.Sk) ? load_bias1<kBf16>(prm.ex, bias_vec, col) : 0.f;
+      // a buffer is rewritten two key tiles later, behind the barrier of the tile between
+      named_barrier_sync(1 + s, 128);
+    };
+    // Issues the tensor-memory loads of step tn's scores (S must be complete).
+    auto issue_load = [&](int tn, int c) {
+      const uint32_t tSn = tS_tile + (tn & 1) * kStepN;
+      tmem_ld32(tSn + c * 32, sr[c]);
+    };
+    // Waits for those loads, applies bias and masks in place and reduces the row maximum.
+    auto finish_loads = [&](int tn) {
+      const int k0n = tn * kStepN;
+      const bool need_mask = (k0n + kStepN > prm.Sk) || (prm.causal && k0n + kStepN - 1 > q0);
+      float mxa = -INFINITY, mxb = -INFINITY, mxc = -INFINITY, mxd = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        tmem_ld_wait(sr[c]);
+        if constexpr (kExt != 0) {
+          if (vec_bias) {
+            const float4* bv = reinterpret_cast<const float4*>(sb + ((tn >> 1) & 1) * 128 + (tn & 1) * kStepN + c * 32);
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              const float4 v4 = bv[i >> 2];  // the same address in every thread: a broadcast
+              sr[c][i + 0] = __float_as_uint(fmaf(__uint_as_float(sr[c][i + 0]), prm.scale_log2, v4.x));
+              sr[c][i + 1] = __float_as_uint(fmaf(__uint_as_float(sr[c][i + 1]), prm.scale_log2, v4.y));
+              sr[c][i + 2] = __float_as_uint(fmaf(__uint_as_float(sr[c][i + 2]), prm.scale_log2, v4.z));
+              sr[c][i + 3] = __float_as_uint(fmaf(__uint_as_float(sr[c][i + 3]), prm.scale_log2, v4.w));
+            }
+          } else if (has_bias) {
+            float bb[32];
+            load_bias32<kBf16>(prm.ex, bias_row, k0n + c * 32, prm.Sk, bb);
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              sr[c][i] = __float_as_uint(fmaf(__uint_as_float(sr[c][i]), prm.scale_log2, bb[i]));
+          }
+        }
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int col = k0n + c * 32 + i;
+            if (col >= prm.Sk || (prm.causal && col > row)) sr[c][i] = 0xff800000u;  // -inf
+          }
+        }
+        // four independent accumulators (and 3-input max) keep the dependency chain short
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+          mxa = max3(mxa, __uint_as_float(sr[c][i + 0]), __uint_as_float(sr[c][i + 1]));
+          mxb = max3(mxb, __uint_as_float(sr[c][i + 2]), __uint_as_float(sr[c][i + 3]));
+          mxc = max3(mxc, __uint_as_float(sr[c][i + 4]), __uint_as_float(sr[c][i + 5]));
+          mxd = max3(mxd, __uint_as_float(sr[c][i + 6]), __uint_as_float(sr[c][i + 7]));
+        }
+      }
+      mx = fmaxf(fmaxf(mxa, mxb), fmaxf(mxc, mxd));
+    };
+
+    // prologue: scores and maximum of step 0
+    if constexpr (kExt != 0) {
+      if (vec_bias) stage_vec_bias(0);
+    }
+    mbar_wait(bar_s_full + 2 * s, 0, cta_abort, dstat, FO_STATUS_TIMEOUT_MMA);
+    tcgen05_fence_after_sync();
+    issue_load(0, 0);
+    issue_load(0, 1);
+    finish_loads(0);
+
+    // Each iteration exponentiates step t and, behind the exponentials, fetches and reduces step
+    // t + 1 (whose S the tensor core finished meanwhile), so that the latencies of the loads, of
+    // the P store and of the barriers overlap instead of adding up.
+    for (int t = 0; t < T_s; ++t) {
+      const int u = t & 1;
+      const int k0 = t * kStepN;
+      const uint32_t tS = tS_tile + u * kStepN;
+      if ((warp & 3) == 0) trace_event(prm, s, t, 0);
+      const float m_cand = fmaxf(m_run, mx * exp_scale);
+      const float m_new = (m_cand - m_run > kRescaleThreshold) ? m_cand : m_run;
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+      const float alpha = (m_new == m_run) ? 1.f : fast_exp2(m_run - m_use);
+      // hand the rescale factor to the correction warps before the exponentials
+      alpha_slot[u * 128] = alpha;
+      mbar_arrive(bar_corr + 2 * s + u);
+      if ((warp & 3) == 0) trace_event(prm, s, t, 1);
+      float neg_m = -m_use;
+      if (ping_pong) named_barrier_sync_dep(s ? kTurn1 : kTurn0, 256, neg_m);  // exponentials start after this
+      if ((warp & 3) == 0) trace_event(prm, s, t, 4);
+      const float2 sc2 = make_float2(exp_scale, exp_scale);
+      const float2 nm2 = make_float2(neg_m, neg_m);
+      float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
+      uint32_t pr[2][16];
+      const bool more = t + 1 < T_s;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+#pragma unroll
+        for (int q = 0; q < 16; ++q) {  // column pair q of the chunk
+          float2 x = __ffma2_rn(make_float2(__uint_as_float(sr[c][2 * q]), __uint_as_float(sr[c][2 * q + 1])), sc2, nm2);
+          x.x = fast_exp2(x.x);
+          x.y = fast_exp2(x.y);
+          if (q & 1) acc1 = __fadd2_rn(acc1, x); else acc0 = __fadd2_rn(acc0, x);
+          if constexpr (kExt != 0) {
+            // dropped elements leave the row sum untouched and enter P V as zeros; the factor
+            // 1 / (1 - p) is applied once, to O, in the epilogue
+            if (has_drop) {
+              const uint32_t idx = drop_row + static_cast<uint32_t>(k0 + c * 32 + 2 * q);
+              if (dropout_hash(idx, prm.ex.drop_seed) <= prm.ex.drop_threshold) x.x = 0.f;
+              if (dropout_hash(idx + 1u, prm.ex.drop_seed) <= prm.ex.drop_threshold) x.y = 0.f;
+            }
+          }
+          pr[c][q] = pack2<kBf16>(x.x, x.y);
+        }
+      }
+      // (the row sums depend on every exponential of the step)
+      if (ping_pong) named_barrier_arrive_dep(s ? kTurn0 : kTurn1, 256, acc0.x + acc0.y, acc1.x + acc1.y);
+      if ((warp & 3) == 0) trace_event(prm, s, t, 2);
+      if (more) {
+        // S of step t + 1 was issued when P of step t - 1 was handed over: complete by now as a rule
+        if constexpr (kExt != 0) {
+          if (vec_bias && u == 1) stage_vec_bias(t + 1);
+          if (!vec_bias && bias_row != nullptr) {
+            const int c0 = k0 + kStepN;
+            prefetch_bias(prm.ex, bias_row, c0, min(kStepN, prm.Sk - c0));
+          }
+        }
+        mbar_wait(bar_s_full + 2 * s + (u ^ 1), ((t + 1) >> 1) & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_MMA);
+        tcgen05_fence_after_sync();
+        issue_load(t + 1, 0);  // the score registers are free: everything of step t is in pr by now
+        issue_load(t + 1, 1);
+      }
+      // P (two 16-bit values per column) over the first 32 columns of this step's buffer
+      tmem_st16(tS, pr[0]);
+      tmem_st16(tS + 16, pr[1]);
+      tcgen05_wait_st();
+      tcgen05_fence_before_sync();
+      mbar_arrive(bar_p_full + 2 * s + u);
+      if ((warp & 3) == 0) trace_event(prm, s, t, 3);
+      const float rsum = (acc0.x + acc0.y) + (acc1.x + acc1.y);
+      l_run = l_run * alpha + rsum;
+      m_run = m_new;
+      if (more) finish_loads(t + 1);
+      if ((warp & 3) == 0) trace_event(prm, s, t, 5);
+    }
+    s_final[s * 256 + r] = l_run;
+    s_final[s * 256 + 128 + r] = m_run;
+    mbar_arrive(bar_final + s);
+    // Keep taking and passing the turn for the steps that only the other tile still has, one at
+    // a time (arrivals sent ahead of the other tile's waits would complete a barrier phase on
+    // their own and strand it).  Tile 1's very last arrival finds nobody waiting: the CTA ends
+    // with that barrier half counted, which is harmless.
+    if (ping_pong && s == 0)
+      for (int t = T0; t < T1; ++t) {
+        named_barrier_sync(kTurn0, 256);
+        named_barrier_arrive(kTurn1, 256);
+      }
+  } else if (warp < 12) {
+    // ================================ correction + epilogue ================================
+    reg_dealloc<80>();
+    const int r = (warp & 3) * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    for (int t = 0; t < T1; ++t) {
+#pragma unroll
+      for (int s = 0; s < 2; ++s) {
+        if (t >= (s ? T1 : T0)) continue;
+        mbar_wait(bar_corr + 2 * s + (t & 1), (t >> 1) & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_SOFTMAX);
+        const float alpha = s_alpha[s * 256 + (t & 1) * 128 + r];
+        if (t > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+          // this step's P V is not issued before this warp arrives below; O is complete up to
+          // the previous step once that step's P V has finished.  (The P V of step t - 2 is
+          // known to have finished, since S of step t exists: the phase bit is unambiguous.)
+          mbar_wait(bar_o_full + s, (t - 1) & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_MMA);
+          tcgen05_fence_after_sync();
+          {
+            const uint32_t tO = tmem_base + Cfg::kColO0 + s * D + lane_base;
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+              uint32_t orr[32];
+              tmem_ld32(tO + c * 32, orr);
+              tmem_ld_wait(orr);
+#pragma unroll
+              for (int i = 0; i < 32; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
+              tmem_st32(tO + c * 32, orr);
+            }
+            tcgen05_wait_st();
+          }
+          tcgen05_fence_before_sync();
+        }
+        mbar_arrive(bar_p_full + 2 * s + (t & 1));
+      }
+    }
+    // epilogue: O / l and LSE
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+      const int T_s = s ? T1 : T0;
+      mbar_wait(bar_final + s, 0, cta_abort, dstat, FO_STATUS_TIMEOUT_SOFTMAX);
+      mbar_wait(bar_o_done + s, 0, cta_abort, dstat, FO_STATUS_TIMEOUT_MMA);
+      tcgen05_fence_after_sync();
+      const float l_run = s_final[s * 256 + r];
+      const float m_run = s_final[s * 256 + 128 + r];
+      const float o_scale = (kExt != 0) ? prm.ex.drop_rescale : 1.f;
+      const float inv_l = (l_run > 0.f) ? o_scale / l_run : 0.f;
+      const int row = (2 * pair + s) * kBlockM + r;
+      const bool row_ok = row < prm.Sq;
+      uint16_t* orow = static_cast<uint16_t*>(prm.o) + b * prm.o_stride_b + h * prm.o_stride_h +
+                       static_cast<int64_t>(row) * prm.o_stride_s;
+      const uint32_t tO = tmem_base + Cfg::kColO0 + s * D + lane_base;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t orr[32];
+        tmem_ld32(tO + c * 32, orr);
+        tmem_ld_wait(orr);
+        if (row_ok) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 v;
+            v.x = pack2<kBf16>(__uint_as_float(orr[i + 0]) * inv_l, __uint_as_float(orr[i + 1]) * inv_l);
+            v.y = pack2<kBf16>(__uint_as_float(orr[i + 2]) * inv_l, __uint_as_float(orr[i + 3]) * inv_l);
+            v.z = pack2<kBf16>(__uint_as_float(orr[i + 4]) * inv_l, __uint_as_float(orr[i + 5]) * inv_l);
+            v.w = pack2<kBf16>(__uint_as_float(orr[i + 6]) * inv_l, __uint_as_float(orr[i + 7]) * inv_l);
+            *reinterpret_cast<uint4*>(orow + c * 32 + i) = v;
+          }
+        }
+      }
+      if (row_ok && prm.lse != nullptr) {
+        prm.lse[static_cast<int64_t>(bh) * prm.Sq + row] =
+            (l_run > 0.f) ? (m_run + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
+      }
+    }
+  } else {
+    reg_dealloc<48>();
+    if (warp == 12 || warp == 14) {
+      // ================================ MMA issuers ================================
+      // One warp per query tile (12: tile 0, 14: tile 1).  The tensor core's instruction queue
+      // is short: whenever the issuing warp is not issuing (a barrier wait costs it about 200
+      // cycles even on a completed phase) the pipe runs dry.  With two issuers one tile's waits
+      // hide behind the other tile's instructions.  Nothing orders the two streams against each
+      // other, and nothing has to: each tile owns its S / P buffers and its O accumulator, and a
+      // K/V ring slot is released by both warps (bar_kv_empty counts two arrivals).
+      const int s = (warp == 14) ? 1 : 0;
+      const int T_s = s ? T1 : T0;
+      constexpr uint32_t idesc_qk = make_idesc(kBf16, kBlockM, kStepN, 0, 0);
+      constexpr uint32_t idesc_pv = make_idesc(kBf16, kBlockM, D, 0, 1);
+      // Everything below is warp-uniform; only the tcgen05 instructions themselves are issued by
+      // one elected lane.  Descriptors are kept as 32-bit low halves: per instruction one add.
+      const uint32_t q_lo = desc_lo(smem_u32(sQ) + s * kTileBytes, 16);
+      const uint32_t kv_k_lo = desc_lo(smem_u32(sKV), 16);         // K tiles: K-major
+      const uint32_t kv_v_lo = desc_lo(smem_u32(sKV), kBoxBytes);  // V tiles: N-major
+      constexpr uint32_t kStageStep = kTileBytes >> 4;
+      constexpr uint32_t kBoxStep = kBoxBytes >> 4;
+      const uint32_t tS_tile = tmem_base + Cfg::kColS0 + s * kBlockN;
+      const uint32_t tO = tmem_base + Cfg::kColO0 + s * D;
+      // S(s, t) = Q_s K^T over keys [64 u, 64 u + 64) of the K tile in ring slot `stage`, u = t & 1:
+      // 64 rows of a K-major box are 64 * 128 bytes further on
+      auto issue_s = [&](int u, int stage) {
+        const uint32_t b_lo = kv_k_lo + stage * kStageStep + u * ((kStepN * 128) >> 4);
+        const uint32_t tS = tS_tile + u * kStepN;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          // k-slice kk: box kk/4, 32 bytes per slice inside the 128-byte swizzle span
+          const uint32_t off = (kk >> 2) * kBoxStep + (kk & 3) * 2;
+          umma_ss_lo_elect(tS, q_lo + off, b_lo + off, idesc_qk, kk > 0 ? 1u : 0u);
+        }
+      };
+      // O_s (+)= P(s, t) V over key rows [64 u, 64 u + 64) of the V tile in ring slot `stage`
+      auto issue_pv = [&](int u, int stage, bool acc) {
+        const uint32_t tP = tS_tile + u * kStepN;
+        const uint32_t b_lo = kv_v_lo + stage * kStageStep + u * (kStepN / 16) * 128;
+#pragma unroll
+        for (int kk = 0; kk < kStepN / 16; ++kk) {
+          // 16 key rows per slice: 2048 bytes of V, 8 packed columns of P
+          umma_ts_lo_elect(tO, tP + kk * 8, b_lo + kk * 128, idesc_pv, (acc || kk > 0) ? 1u : 0u);
+        }
+      };
+
+      mbar_wait(bar_q_full, 0, cta_abort, dstat, FO_STATUS_TIMEOUT_TMA);
+      mbar_wait(bar_kv_full + 0, 0, cta_abort, dstat, FO_STATUS_TIMEOUT_TMA);  // K_0 is ring slot 0
+      tcgen05_fence_after_sync();
+      // prologue: the first two steps, both on K_0
+      issue_s(0, 0);
+      tcgen05_commit_elect(bar_s_full + 2 * s);
+      if (T_s > 1) {
+        issue_s(1, 0);
+        tcgen05_commit_elect(bar_s_full + 2 * s + 1);
+      }
+      tcgen05_commit_elect(bar_kv_empty + 0);
+      // Barriers are polled (without blocking) one iteration ahead and waited on only if the
+      // poll failed.
+      bool p_ready = false, kv_ready = false;
+      for (int t = 0; t < T1; ++t) {  // both warps walk all key tiles: the ring needs both
+        const int j = t >> 1, u = t & 1;
+        const int iv = 2 * j + 1;  // ring index of V_j; K_{j+1} is iv + 1
+        const int st_v = iv % kStages;
+        const int st_k = (iv + 1) % kStages;
+        const bool k_next = j + 1 < n1;  // K_{j+1} exists
+        if (u == 0 && !kv_ready) {
+          mbar_wait(bar_kv_full + st_v, (iv / kStages) & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_TMA);
+          if (k_next) mbar_wait(bar_kv_full + st_k, ((iv + 1) / kStages) & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_TMA);
+        }
+        if (s == 0) trace_event(prm, 2, t, 0);
+        kv_ready = false;
+        if (t < T_s) {
+          if (!p_ready)
+            mbar_wait(bar_p_full + 2 * s + u, (t >> 1) & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_SOFTMAX);
+          tcgen05_fence_after_sync();
+          if (s == 0) trace_event(prm, 2, t, 1);
+          issue_pv(u, st_v, t > 0);
+          tcgen05_commit_elect(bar_o_full + s);
+          if (t + 1 == T_s) tcgen05_commit_elect(bar_o_done + s);
+          if (s == 0) trace_event(prm, 2, t, 2);
+          // step t + 2 goes into the buffer that P(s, t) is being read from; the tensor core runs
+          // one thread's instructions in order, so the read comes first
+          if (t + 2 < T_s) {
+            issue_s(u, st_k);
+            tcgen05_commit_elect(bar_s_full + 2 * s + u);
+          }
+          if (s == 0) trace_event(prm, 2, t, 3);
+          p_ready = (t + 1 < T_s) && mbar_test_wait(bar_p_full + 2 * s + (u ^ 1), ((t + 1) >> 1) & 1);
+        }
+        if (u == 1 || t + 1 == T1) {
+          // this warp's readers of V_j (and of K_{j+1}) have all been issued
+          tcgen05_commit_elect(bar_kv_empty + st_v);
+          if (k_next) tcgen05_commit_elect(bar_kv_empty + st_k);
+          if (t + 1 < T1) {
+            const int iv2 = iv + 2;
+            kv_ready = mbar_test_wait(bar_kv_full + iv2 % kStages, (iv2 / kStages) & 1) &&
+                       (!(j + 2 < n1) || mbar_test_wait(bar_kv_full + (iv2 + 1) % kStages, ((iv2 + 1) / kStages) & 1));
+          }
+        }
+      }
+    } else if (warp == 13) {
+      // ================================ TMA producer ================================
+      const bool issuer = lane == 0;
+      if (issuer) {
+        mbar_arrive_expect_tx(bar_q_full, 2 * kTileBytes);
+        for (int s = 0; s < 2; ++s)
+          for (int c = 0; c < kBoxes; ++c)
+            tma_load_4d(sQ + s * kTileBytes + c * kBoxBytes, &tm_q, bar_q_full, c * kBoxCols,
+                        (2 * pair + s) * kBlockM, h, b);
+      }
+      __syncwarp();
+      for (int i = 0; i < 2 * n1; ++i) {
+        const int st = i % kStages;
+        mbar_wait(bar_kv_empty + st, ((i / kStages) & 1) ^ 1, cta_abort, dstat, FO_STATUS_TIMEOUT_MMA);
+        if (issuer) {
+          mbar_arrive_expect_tx(bar_kv_full + st, kTileBytes);
+          const CUtensorMap* map = (i & 1) ? &tm_v : &tm_k;
+          for (int c = 0; c < kBoxes; ++c)
+            tma_load_4d(sKV + st * kTileBytes + c * kBoxBytes, map, bar_kv_full + st, c * kBoxCols,
+                        (i >> 1) * kBlockN, hk, b);
+        }
+        __syncwarp();
+      }
+    }
+  }
+
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  if (warp == 12) tmem_dealloc(tmem_base, Cfg::kTmemCols);
+}
+
+template <int D, bool kBf16, int kExt>
+int launch_ws64(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& prm,
+                cudaStream_t stream) {
+  auto kernel = attn_fwd_ws64_kernel<D, kBf16, kExt>;
+  constexpr int smem = Ws64Config<D>::kSmemBytes;
+  cudaError_t ea = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (ea != cudaSuccess)
+    return fail(FO_ERR_CUDA, "cudaFuncSetAttribute(shared memory %d) failed: %s", smem, cudaGetErrorString(ea));
+  const int num_pairs = (prm.num_q_tiles + 1) / 2;
+  const int64_t blocks = static_cast<int64_t>(num_pairs) * prm.B * prm.H;
+  if (blocks > 0x7fffffffLL) return fail(FO_ERR_INVALID_ARGUMENT, "too many query tiles for one launch");
+  kernel<<<static_cast<unsigned>(blocks), 512, smem, stream>>>(tq, tk, tv, prm);
+  g_launch_count.fetch_add(1, std::memory_order_relaxed);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(FO_ERR_CUDA, "attention launch failed: %s", cudaGetErrorString(e));
+  return FO_OK;
+}
+
+}  // namespace fo

@@ -56,6 +56,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Non-blocking poll of a phase (try_wait may suspend the thread for a while when the phase is
+// still open; test_wait returns at once).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Bounded wait.  Every wait in the attention kernels goes through here: it spins on
 // try_wait, and once `kWaitBudgetNs` of wall time has passed it records `code` in the
 // CTA's abort word (shared memory) and in the device status word and returns false.  From
@@ -66,8 +82,9 @@ constexpr uint64_t kWaitBudgetNs = 1000ull * 1000ull * 1000ull;  // 1 s
 
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* cta_abort,
                                           int* device_status, int code) {
-  if (*cta_abort) return false;
+  // the common case first: a completed phase costs one try_wait and no shared-memory load
   if (mbar_try_wait(bar, parity)) return true;
+  if (*cta_abort) return false;
   const uint64_t t0 = global_timer_ns();
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
@@ -130,6 +147,22 @@ __device__ __forceinline__ void prefetch_l2(const void* p) {
 // bar.sync on a named barrier (id 1..15) among `count` threads of the CTA
 __device__ __forceinline__ void named_barrier_sync(int id, int count) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+
+// bar.arrive: counts this thread in on a named barrier without waiting for it
+__device__ __forceinline__ void named_barrier_arrive(int id, int count) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+
+// The same two operations tied into the data flow, for use as scheduling fences around pure
+// arithmetic (which the compiler otherwise moves freely across a barrier): the sync form
+// "produces" `dep`, so nothing computed from it can start earlier; the arrive form "consumes"
+// its operands, so it cannot be issued before they have been computed.
+__device__ __forceinline__ void named_barrier_sync_dep(int id, int count, float& dep) {
+  asm volatile("bar.sync %1, %2;" : "+f"(dep) : "r"(id), "r"(count) : "memory");
+}
+__device__ __forceinline__ void named_barrier_arrive_dep(int id, int count, float a, float b) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(count), "f"(a), "f"(b) : "memory");
 }
 
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
