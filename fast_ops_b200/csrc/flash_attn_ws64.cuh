@@ -211,6 +211,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         tmem_ld_wait(sr[c]);
+        if ((warp & 3) == 0 && tn > 0) trace_event(prm, s, tn - 1, c == 0 ? 1 : 4);  // loads in / half reduced
         if constexpr (kExt != 0) {
           if (vec_bias) {
             const float4* bv = reinterpret_cast<const float4*>(sb + ((tn >> 1) & 1) * 128 + (tn & 1) * kStepN + c * 32);
@@ -266,7 +267,6 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       const int u = t & 1;
       const int k0 = t * kStepN;
       const uint32_t tS = tS_tile + u * kStepN;
-      if ((warp & 3) == 0) trace_event(prm, s, t, 0);
       const float m_cand = fmaxf(m_run, mx * exp_scale);
       const float m_new = (m_cand - m_run > kRescaleThreshold) ? m_cand : m_run;
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
@@ -274,17 +274,20 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       // hand the rescale factor to the correction warps before the exponentials
       alpha_slot[u * 128] = alpha;
       mbar_arrive(bar_corr + 2 * s + u);
-      if ((warp & 3) == 0) trace_event(prm, s, t, 1);
       float neg_m = -m_use;
       if (ping_pong) named_barrier_sync_dep(s ? kTurn1 : kTurn0, 256, neg_m);  // exponentials start after this
-      if ((warp & 3) == 0) trace_event(prm, s, t, 4);
+      if ((warp & 3) == 0) trace_event(prm, s, t, 0);  // turn taken
       const float2 sc2 = make_float2(exp_scale, exp_scale);
       const float2 nm2 = make_float2(neg_m, neg_m);
       float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
       uint32_t pr[2][16];
       const bool more = t + 1 < T_s;
+      bool s_next_ready = false;
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
+        // one non-blocking look at S of step t + 1 (as a rule complete by now); the answer is
+        // needed only after the exponentials, so its latency is hidden
+        if (c == 1 && more) s_next_ready = mbar_test_wait(bar_s_full + 2 * s + (u ^ 1), ((t + 1) >> 1) & 1);
 #pragma unroll
         for (int q = 0; q < 16; ++q) {  // column pair q of the chunk
           float2 x = __ffma2_rn(make_float2(__uint_as_float(sr[c][2 * q]), __uint_as_float(sr[c][2 * q + 1])), sc2, nm2);
@@ -306,8 +309,13 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       // (the row sums depend on every exponential of the step)
       if (ping_pong) named_barrier_arrive_dep(s ? kTurn0 : kTurn1, 256, acc0.x + acc0.y, acc1.x + acc1.y);
       if ((warp & 3) == 0) trace_event(prm, s, t, 2);
+      // P (two 16-bit values per column) over the first 32 columns of this step's buffer
+      tmem_st16(tS, pr[0]);
+      tmem_st16(tS + 16, pr[1]);
       if (more) {
-        // S of step t + 1 was issued when P of step t - 1 was handed over: complete by now as a rule
+        // S of step t + 1 was issued when P of step t - 1 was handed over: complete by now as a
+        // rule.  Its loads go out behind the P stores; the score registers are free, everything
+        // of step t is in pr.
         if constexpr (kExt != 0) {
           if (vec_bias && u == 1) stage_vec_bias(t + 1);
           if (!vec_bias && bias_row != nullptr) {
@@ -315,14 +323,12 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             prefetch_bias(prm.ex, bias_row, c0, min(kStepN, prm.Sk - c0));
           }
         }
-        mbar_wait(bar_s_full + 2 * s + (u ^ 1), ((t + 1) >> 1) & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_MMA);
+        if (!s_next_ready)
+          mbar_wait(bar_s_full + 2 * s + (u ^ 1), ((t + 1) >> 1) & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_MMA);
         tcgen05_fence_after_sync();
-        issue_load(t + 1, 0);  // the score registers are free: everything of step t is in pr by now
+        issue_load(t + 1, 0);
         issue_load(t + 1, 1);
       }
-      // P (two 16-bit values per column) over the first 32 columns of this step's buffer
-      tmem_st16(tS, pr[0]);
-      tmem_st16(tS + 16, pr[1]);
       tcgen05_wait_st();
       tcgen05_fence_before_sync();
       mbar_arrive(bar_p_full + 2 * s + u);
