@@ -276,14 +276,15 @@ static int attn_fwd_impl(const void* q, const void* k, const void* v, void* o, f
   const bool bf16 = dtype == FO_BF16;
   AttnImpl impl = chosen_impl();
   if (impl == AttnImpl::kAuto) {
-    // The 64-key-step kernel fills and drains its pipeline faster (S is double-buffered, one MMA
-    // issuer per query tile) and wins while a CTA sees few key tiles; in a long steady state the
-    // 128-key kernel's fewer, larger steps win.  Measured crossover: about 24 key tiles per CTA on
-    // average (causal S = 8192 is a tie; causal S <= 4096 gains 7-35 %).
+    // The 64-key-step kernel is the faster one at every shape measured (same box, hot loop, bf16
+    // causal: S=16384 1.11 against 1.02 PFLOP/s, S=4096 0.98 against 0.82, GPT-2-small shape
+    // 0.29 against 0.21); the 128-key kernel stays selectable.
+    impl = AttnImpl::kWarpSpecialized64;
+    // one exception, also measured: with a bias and no dropout, over a long key range, the
+    // 128-key kernel is about 7 % ahead (0.79 against 0.73 PFLOP/s at S=16384)
     const int n_kv = (Sk + kBlockN - 1) / kBlockN;
-    const int avg_tiles = causal ? (n_kv + 1) / 2 : n_kv;
-    // With a bias or dropout the 64-key kernel is as fast or faster at every length measured.
-    impl = (ext || avg_tiles <= 24) ? AttnImpl::kWarpSpecialized64 : AttnImpl::kWarpSpecialized;
+    const bool bias_only = ext && ex->bias != nullptr && !ex->dropout;
+    if (bias_only && (causal ? (n_kv + 1) / 2 : n_kv) > 48) impl = AttnImpl::kWarpSpecialized;
   }
   const int mode = ext ? ((prm.ex.bias != nullptr ? 1 : 0) | (prm.ex.dropout ? 2 : 0)) : 0;
   // bias and dropout exist in the warp-specialised kernels only

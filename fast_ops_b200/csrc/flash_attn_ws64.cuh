@@ -288,6 +288,10 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         // one non-blocking look at S of step t + 1 (as a rule complete by now); the answer is
         // needed only after the exponentials, so its latency is hidden
         if (c == 1 && more) s_next_ready = mbar_test_wait(bar_s_full + 2 * s + (u ^ 1), ((t + 1) >> 1) & 1);
+        // The turn is passed on after the first half (the partial row sums depend on all of its
+        // exponentials): the other tile's first half then shares the ex2 units with this tile's
+        // second half, two warps per scheduler, which hides the latencies a lone warp exposes.
+        if (c == 1 && ping_pong) named_barrier_arrive_dep(s ? kTurn0 : kTurn1, 256, acc0.x + acc0.y, acc1.x + acc1.y);
 #pragma unroll
         for (int q = 0; q < 16; ++q) {  // column pair q of the chunk
           float2 x = __ffma2_rn(make_float2(__uint_as_float(sr[c][2 * q]), __uint_as_float(sr[c][2 * q + 1])), sc2, nm2);
@@ -306,8 +310,6 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           pr[c][q] = pack2<kBf16>(x.x, x.y);
         }
       }
-      // (the row sums depend on every exponential of the step)
-      if (ping_pong) named_barrier_arrive_dep(s ? kTurn0 : kTurn1, 256, acc0.x + acc0.y, acc1.x + acc1.y);
       if ((warp & 3) == 0) trace_event(prm, s, t, 2);
       // P (two 16-bit values per column) over the first 32 columns of this step's buffer
       tmem_st16(tS, pr[0]);
