@@ -26,6 +26,7 @@ namespace fo {
 
 constexpr int kStepN = 64;  // keys per softmax step
 
+
 template <int D>
 struct Ws64Config : WsConfig<D> {
   // barriers: q_full, kv_full/empty per stage, then s_full[2][2], p_full[2][2], o_full[2],
@@ -182,9 +183,9 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     // exponentials of the two tiles are therefore made to alternate with a pair of named barriers
     // (tile 0 goes first): while one tile exponentiates, the other loads S, reduces its maxima
     // and stores P.  A tile that runs out of steps keeps passing the turn on.
-    constexpr int kTurn0 = 3, kTurn1 = 4;  // named barriers: "tile 0 may exponentiate", "tile 1 may"
+    constexpr int kTurn0 = 3, kTurn1 = 4, kTurnCount = 256;  // named barriers: "tile 0 may exponentiate", "tile 1 may"
     const bool ping_pong = prm.ping_pong != 0;
-    if (ping_pong && s == 1) named_barrier_arrive(kTurn0, 256);
+    if (ping_pong && s == 1) named_barrier_arrive(kTurn0, kTurnCount);
 
     uint32_t sr[2][32];  // scores of the current step (scaled and biased already when there is a bias)
     float mx = -INFINITY;  // their row maximum
@@ -270,12 +271,17 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       const float m_cand = fmaxf(m_run, mx * exp_scale);
       const float m_new = (m_cand - m_run > kRescaleThreshold) ? m_cand : m_run;
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      const float alpha = (m_new == m_run) ? 1.f : fast_exp2(m_run - m_use);
-      // hand the rescale factor to the correction warps before the exponentials
+      // The rescale factor is 1 for every row of the warp in nearly all steps (lazy rescaling):
+      // a warp-uniform branch keeps its ex2 out of the way then.  It would otherwise queue behind
+      // the other tile's exponentials on the same unit and, issue being in order, hold up
+      // everything below.
+      float alpha = 1.f;
+      if (__any_sync(0xffffffffu, m_new != m_run)) alpha = (m_new == m_run) ? 1.f : fast_exp2(m_run - m_use);
+      float neg_m = -m_use;
+      if (ping_pong) named_barrier_sync_dep(s ? kTurn1 : kTurn0, kTurnCount, neg_m);  // exponentials start after this
+      // hand the rescale factor to the correction warps (off this thread's critical path)
       alpha_slot[u * 128] = alpha;
       mbar_arrive(bar_corr + 2 * s + u);
-      float neg_m = -m_use;
-      if (ping_pong) named_barrier_sync_dep(s ? kTurn1 : kTurn0, 256, neg_m);  // exponentials start after this
       if ((warp & 3) == 0) trace_event(prm, s, t, 0);  // turn taken
       const float2 sc2 = make_float2(exp_scale, exp_scale);
       const float2 nm2 = make_float2(neg_m, neg_m);
@@ -291,10 +297,14 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         // The turn is passed on after the first half (the partial row sums depend on all of its
         // exponentials): the other tile's first half then shares the ex2 units with this tile's
         // second half, two warps per scheduler, which hides the latencies a lone warp exposes.
-        if (c == 1 && ping_pong) named_barrier_arrive_dep(s ? kTurn0 : kTurn1, 256, acc0.x + acc0.y, acc1.x + acc1.y);
+        float2 nm2c = nm2;
+        if (c == 1 && ping_pong) {
+          named_barrier_arrive_mid(s ? kTurn0 : kTurn1, kTurnCount, neg_m, acc0.x + acc0.y, acc1.x + acc1.y);
+          nm2c = make_float2(neg_m, neg_m);  // the second half's arithmetic hangs on the arrive
+        }
 #pragma unroll
         for (int q = 0; q < 16; ++q) {  // column pair q of the chunk
-          float2 x = __ffma2_rn(make_float2(__uint_as_float(sr[c][2 * q]), __uint_as_float(sr[c][2 * q + 1])), sc2, nm2);
+          float2 x = __ffma2_rn(make_float2(__uint_as_float(sr[c][2 * q]), __uint_as_float(sr[c][2 * q + 1])), sc2, nm2c);
           x.x = fast_exp2(x.x);
           x.y = fast_exp2(x.y);
           if (q & 1) acc1 = __fadd2_rn(acc1, x); else acc0 = __fadd2_rn(acc0, x);
@@ -350,8 +360,8 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     // with that barrier half counted, which is harmless.
     if (ping_pong && s == 0)
       for (int t = T0; t < T1; ++t) {
-        named_barrier_sync(kTurn0, 256);
-        named_barrier_arrive(kTurn1, 256);
+        named_barrier_sync(kTurn0, kTurnCount);
+        named_barrier_arrive(kTurn1, kTurnCount);
       }
   } else if (warp < 12) {
     // ================================ correction + epilogue ================================

@@ -164,6 +164,11 @@ __device__ __forceinline__ void named_barrier_sync_dep(int id, int count, float&
 __device__ __forceinline__ void named_barrier_arrive_dep(int id, int count, float a, float b) {
   asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(count), "f"(a), "f"(b) : "memory");
 }
+// Arrive that is pinned on both sides: it consumes a and b and "produces" dep, so arithmetic that
+// uses dep afterwards cannot be scheduled in front of it either.
+__device__ __forceinline__ void named_barrier_arrive_mid(int id, int count, float& dep, float a, float b) {
+  asm volatile("bar.arrive %1, %2;" : "+f"(dep) : "r"(id), "r"(count), "f"(a), "f"(b) : "memory");
+}
 
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Waits until the shared-memory source of all committed stores has been read.
