@@ -106,11 +106,9 @@ static int attn_bwd_impl(const void* q, const void* k, const void* v, const void
   FO_REQUIRE(dtype == FO_F16 || dtype == FO_BF16, "attention tensors must be fp16 or bf16 (got dtype %d)", dtype);
   FO_REQUIRE(B > 0 && H > 0 && Sq > 0 && Sk > 0, "B, H, Sq, Sk must be positive");
   FO_REQUIRE(static_cast<int64_t>(B) * H <= 65535, "B*H must be <= 65535");
-  if (D != 64 && D != 128) {
-    if (D <= 0 || D > 128 || D % 8 != 0)
-      return fo::fail(FO_ERR_INVALID_ARGUMENT, "head_dim must be a multiple of 8 and <= 128 (got %d)", D);
-    return fo::fail(FO_ERR_UNSUPPORTED, "head_dim %d has no kernel in this build (64 and 128 do)", D);
-  }
+  if (D <= 0 || D > 128 || D % 8 != 0)
+    return fo::fail(FO_ERR_INVALID_ARGUMENT, "head_dim must be a multiple of 8 and <= 128 (got %d)", D);
+  const int Dk = D <= 64 ? 64 : 128;  // head_dim the kernel is built for
   FO_REQUIRE(softmax_scale > 0.f && std::isfinite(softmax_scale), "softmax_scale must be positive and finite");
   for (const void* p : {static_cast<const void*>(o), static_cast<const void*>(dq), static_cast<const void*>(dk),
                         static_cast<const void*>(dv)})
@@ -167,6 +165,7 @@ static int attn_bwd_impl(const void* q, const void* k, const void* v, const void
   prm.H = H;
   prm.Sq = Sq;
   prm.Sk = Sk;
+  prm.d_real = D;
   prm.causal = causal ? 1 : 0;
   prm.scale = softmax_scale;
   prm.scale_log2 = softmax_scale * 1.4426950408889634f;
@@ -180,7 +179,7 @@ static int attn_bwd_impl(const void* q, const void* k, const void* v, const void
   const int mode = ext ? ((prm.ex.bias != nullptr ? 1 : 0) | (prm.ex.dropout ? 2 : 0)) : 0;
 #define FO_BWD_MODE(M)                                                                                     \
   case M:                                                                                                  \
-    if (D == 128) rc = bf16 ? launch_bwd<128, true, M>(tq, tk, tv, tdo, tdq, prm, s) : launch_bwd<128, false, M>(tq, tk, tv, tdo, tdq, prm, s); \
+    if (Dk == 128) rc = bf16 ? launch_bwd<128, true, M>(tq, tk, tv, tdo, tdq, prm, s) : launch_bwd<128, false, M>(tq, tk, tv, tdo, tdq, prm, s); \
     else rc = bf16 ? launch_bwd<64, true, M>(tq, tk, tv, tdo, tdq, prm, s) : launch_bwd<64, false, M>(tq, tk, tv, tdo, tdq, prm, s);            \
     break;
   switch (mode) {

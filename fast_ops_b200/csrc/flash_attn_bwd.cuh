@@ -38,6 +38,7 @@ struct AttnBwdParams {
   int64_t dk_stride_b, dk_stride_h, dk_stride_s;
   int64_t dv_stride_b, dv_stride_h, dv_stride_s;
   int B, H, Sq, Sk;
+  int d_real;  // head_dim of the tensors (<= the kernel's D; the missing columns are zero-filled by TMA)
   int causal;
   float scale;       // softmax scale
   float scale_log2;  // scale * log2(e)
@@ -331,7 +332,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       named_barrier_sync(1, 256);
       if (tid == 0) {
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) tma_reduce_add_3d(&tm_dq, sP + c * kBoxBytes, c * 32, q0, bh);
+        for (int c = 0; c < D / 32; ++c)
+          if (c * 32 < prm.d_real) tma_reduce_add_3d(&tm_dq, sP + c * kBoxBytes, c * 32, q0, bh);
         tma_store_commit();
       }
     }
@@ -373,7 +375,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             v.y = pack2<kBf16>(__uint_as_float(ar[x + 2]), __uint_as_float(ar[x + 3]));
             v.z = pack2<kBf16>(__uint_as_float(ar[x + 4]), __uint_as_float(ar[x + 5]));
             v.w = pack2<kBf16>(__uint_as_float(ar[x + 6]), __uint_as_float(ar[x + 7]));
-            *reinterpret_cast<uint4*>(out_row + c * 32 + x) = v;
+            if (c * 32 + x < prm.d_real) *reinterpret_cast<uint4*>(out_row + c * 32 + x) = v;
           }
         }
       }

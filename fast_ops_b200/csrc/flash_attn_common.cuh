@@ -90,6 +90,10 @@ struct AttnParams {
   float* lse;  // may be null
   int64_t o_stride_b, o_stride_h, o_stride_s;  // elements
   int B, H, Sq, Sk;
+  // head_dim of the tensors; the kernels are built for 64 and 128, smaller multiples of 8 run in
+  // the next larger one: TMA fills the missing columns of Q, K, V with zeros (they add nothing
+  // to Q K^T and give zero columns of O), and only d_real columns are written back
+  int d_real;
   int causal;
   float scale_log2;  // softmax_scale * log2(e)
   int* device_status;

@@ -209,11 +209,9 @@ static int attn_fwd_impl(const void* q, const void* k, const void* v, void* o, f
   FO_REQUIRE(dtype == FO_F16 || dtype == FO_BF16, "attention inputs must be fp16 or bf16 (got dtype %d)", dtype);
   FO_REQUIRE(B > 0 && H > 0 && Sq > 0 && Sk > 0, "B, H, Sq, Sk must be positive (got %d %d %d %d)", B, H, Sq, Sk);
   FO_REQUIRE(static_cast<int64_t>(B) * H <= 65535, "B*H must be <= 65535 (got %lld)", (long long)B * H);
-  if (D != 64 && D != 128) {
-    if (D <= 0 || D > 128 || D % 8 != 0)
-      return fo::fail(FO_ERR_INVALID_ARGUMENT, "head_dim must be a multiple of 8 and <= 128 (got %d)", D);
-    return fo::fail(FO_ERR_UNSUPPORTED, "head_dim %d has no kernel in this build (64 and 128 do)", D);
-  }
+  if (D <= 0 || D > 128 || D % 8 != 0)
+    return fo::fail(FO_ERR_INVALID_ARGUMENT, "head_dim must be a multiple of 8 and <= 128 (got %d)", D);
+  const int Dk = D <= 64 ? 64 : 128;  // head_dim the kernel is built for
   FO_REQUIRE(softmax_scale > 0.f && std::isfinite(softmax_scale), "softmax_scale must be positive and finite");
   FO_REQUIRE((reinterpret_cast<uintptr_t>(o) & 15) == 0, "o must be 16-byte aligned");
   for (int i = 0; i < 3; ++i)
@@ -246,6 +244,7 @@ static int attn_fwd_impl(const void* q, const void* k, const void* v, void* o, f
   prm.H = H;
   prm.Sq = Sq;
   prm.Sk = Sk;
+  prm.d_real = D;
   prm.causal = causal ? 1 : 0;
   prm.scale_log2 = softmax_scale * 1.4426950408889634f;
   prm.device_status = status;
@@ -290,7 +289,7 @@ static int attn_fwd_impl(const void* q, const void* k, const void* v, void* o, f
   // bias and dropout exist in the warp-specialised kernels only
 #define FO_WS_MODE(LAUNCH, M)                                                                          \
   if (mode == M) {                                                                                     \
-    if (D == 128) return bf16 ? fo::LAUNCH<128, true, M>(tq, tk, tv, prm, s) : fo::LAUNCH<128, false, M>(tq, tk, tv, prm, s); \
+    if (Dk == 128) return bf16 ? fo::LAUNCH<128, true, M>(tq, tk, tv, prm, s) : fo::LAUNCH<128, false, M>(tq, tk, tv, prm, s); \
     return bf16 ? fo::LAUNCH<64, true, M>(tq, tk, tv, prm, s) : fo::LAUNCH<64, false, M>(tq, tk, tv, prm, s);                 \
   }
   if (impl == AttnImpl::kWarpSpecialized64) {
@@ -306,7 +305,7 @@ static int attn_fwd_impl(const void* q, const void* k, const void* v, void* o, f
     FO_WS_MODE(launch_ws, 3)
   }
 #undef FO_WS_MODE
-  if (D == 128) return bf16 ? launch_simple<128, true>(tq, tk, tv, prm, s) : launch_simple<128, false>(tq, tk, tv, prm, s);
+  if (Dk == 128) return bf16 ? launch_simple<128, true>(tq, tk, tv, prm, s) : launch_simple<128, false>(tq, tk, tv, prm, s);
   return bf16 ? launch_simple<64, true>(tq, tk, tv, prm, s) : launch_simple<64, false>(tq, tk, tv, prm, s);
 }
 

@@ -427,7 +427,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             v.y = pack2<kBf16>(__uint_as_float(orr[i + 2]) * inv_l, __uint_as_float(orr[i + 3]) * inv_l);
             v.z = pack2<kBf16>(__uint_as_float(orr[i + 4]) * inv_l, __uint_as_float(orr[i + 5]) * inv_l);
             v.w = pack2<kBf16>(__uint_as_float(orr[i + 6]) * inv_l, __uint_as_float(orr[i + 7]) * inv_l);
-            *reinterpret_cast<uint4*>(orow + c * 32 + i) = v;
+            if (c * 32 + i < prm.d_real) *reinterpret_cast<uint4*>(orow + c * 32 + i) = v;
           }
         }
       }

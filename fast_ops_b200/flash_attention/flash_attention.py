@@ -92,7 +92,7 @@ def flash_attention_forward(Q: Tensor, K: Tensor, V: Tensor, *, causal: bool = F
     (B, H); -inf entries mask.  `dropout_p` > 0 drops attention probabilities with the reference's
     counter-based mask; `rng` = (seed, offset) must then be given (see `next_dropout_rng`).
 
-    Q: (B, H, M, D); K, V: (B, H, N, D); fp16 or bf16; D in {64, 128}; the last dimension
+    Q: (B, H, M, D); K, V: (B, H, N, D); fp16 or bf16; D a multiple of 8 up to 128; the last dimension
     contiguous, the others with strides that are multiples of 8 elements (so (B, S, H, D)
     tensors viewed as (B, H, S, D) are accepted without a copy).  K and V may be expanded over the
     head dimension (stride 0: multi-query attention); the shared head is then read once per tile
@@ -276,8 +276,9 @@ def multi_head_attention(Q: Tensor, K: Tensor, V: Tensor, *, causal: bool = Fals
     :param Q: (B, H, M, D) query.  :param K: (B, H, N, D) key.  :param V: (B, H, N, D) value.
     :returns: (B, H, M, D), or (O, LSE) when `return_lse`.
 
-    Limitations (violations raise RuntimeError): head_dim 64 or 128 in this build (the
-    reference states <= 128 and a multiple of 8); fp16 / bf16 inputs; last dimension
+    Limitations (violations raise RuntimeError), the reference's own: head_dim <= 128 and a
+    multiple of 8 (the kernels are built for 64 and 128, other values run zero-padded in the next
+    larger one); fp16 / bf16 inputs; last dimension
     contiguous.  The scale is 1/sqrt(D) unless `softmax_scale` is given.  `bias` and `dropout_p`
     as in `flash_attention_forward`; the dropout mask is drawn from the device's default generator.
     """

@@ -59,7 +59,9 @@ int fo_device_status(int device, int* status_out, int reset);
  *   *_strides  : element strides of the batch, head and sequence dimensions
  *                (in that order); the head_dim stride is 1.  Each stride must
  *                be a multiple of 8 elements (16 bytes).
- *   D          : 64 or 128.
+ *   D          : a multiple of 8, at most 128 (the reference's contract,
+ *                fast_ops/flash_attention/flash_attention.py:61-70).  The kernels are built for 64
+ *                and 128; other values run zero-padded in the next larger one.
  *   causal     : non-zero masks column j > row i (top-left aligned).
  *   softmax_scale : multiplies Q K^T; pass 1/sqrt(D) for the reference default.
  */

@@ -173,3 +173,19 @@ def test_multi_query_expanded_kv(cuda_device, impl):
     torch.cuda.synchronize()
     assert (out.cpu().float() - ref).abs().max().item() <= TOL[torch.bfloat16]
     assert (lse.cpu() - ref_lse).abs().max().item() <= LSE_TOL
+
+
+@pytest.mark.parametrize("D", [8, 32, 40, 80, 96, 120])
+@pytest.mark.parametrize("causal", [False, True])
+def test_other_head_dims_run_zero_padded(cuda_device, impl, D, causal):
+    """The reference's contract is D <= 128, D % 8 == 0 (fast_ops/flash_attention/flash_attention.py:61-70);
+    the kernels are built for 64 and 128 and take the others with TMA zero-fill."""
+    B, H, Sq, Sk = 2, 2, 200, 333
+    dtype = torch.bfloat16 if D % 16 else torch.float16
+    q, k, v = attention_inputs(50 + D, B, H, Sq, Sk, D, dtype)
+    want, lse_want = oracle.attention_fwd(q, k, v, causal=causal)
+    out, lse = flash_attention_forward(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device), causal=causal,
+                                       return_lse=True)
+    tol = 1e-2 if dtype == torch.bfloat16 else 2e-3
+    assert (out.float().cpu() - want).abs().max().item() <= tol
+    assert (lse.cpu() - lse_want).abs().max().item() <= 1e-3

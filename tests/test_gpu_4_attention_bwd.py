@@ -109,3 +109,13 @@ def test_backward_multi_query_sums_over_heads(cuda_device):
     for name, g, w in zip(("dq", "dk", "dv"), (qd.grad, kd.grad, vd.grad), want):
         err = (g.float().cpu() - w).abs().max().item()
         assert err <= 0.03 * max(1.0, w.abs().max().item()), f"{name}: {err}"
+
+
+@pytest.mark.parametrize("D", [32, 80, 96])
+def test_backward_other_head_dims(cuda_device, D):
+    B, H, Sq, Sk = 1, 2, 200, 300
+    q, k, v = attention_inputs(70 + D, B, H, Sq, Sk, D, torch.bfloat16)
+    dout = attention_dout(70 + D, B, H, Sq, D, torch.bfloat16)
+    want = oracle.attention_bwd(q, k, v, dout, causal=True)
+    got, same = run_backward(q, k, v, dout, True, cuda_device)
+    check(got, same, want, f"D={D}")
