@@ -314,6 +314,22 @@ def bench_attention_variants(d: Dist, name: str, steps: int, warmup: int, peaks)
     return out
 
 
+def bench_attention_sweep(d: Dist, steps: int, warmup: int, peaks):
+    """The metric's sweep: bf16 causal forward, H=32, D=128, batch x sequence = 32768 tokens, so that
+    every point reads the same 805 MB (larger than L2): TFLOP/s per GPU by sequence length."""
+    from fast_ops_b200.flash_attention import flash_attention_forward
+
+    out = {"workload": "attention fwd bf16 causal, H=32 D=128, B*S=32768 tokens per GPU", "unit": "TFLOP/s per GPU"}
+    for S in (1024, 2048, 4096, 8192, 16384):
+        B = 32768 // S
+        q, k, v = attn_inputs(B, 32, S, 128, d.device, seed=7000 + S + d.rank)
+        ms, _ = timed_steps(d, lambda: flash_attention_forward(q, k, v, causal=True), steps, warmup)
+        tf = attn_flops(B, 32, S, 128, True) / (ms * 1e-3) / 1e12
+        out[f"S{S}"] = {"value": tf, "ms_per_step": ms, "frac": tf / peaks["bf16_tflops"]}
+        del q, k, v
+    return out
+
+
 def cpu_attention_sample(name: str, row_stride: int, reps: int):
     """Times the CPU oracle on one (batch, head) slice of the workload, every `row_stride`-th
     query row (the causal row costs are sampled evenly), all host threads."""
@@ -581,6 +597,7 @@ def main():
         if not args.workload.startswith("attn_bwd"):
             also["attn_bwd_c3"] = bench_attention_bwd(d, "attn_c3", max(3, args.steps // 4), 2, peaks)
             also["attn_bias_dropout_c3"] = bench_attention_variants(d, "attn_c3", max(3, args.steps // 4), 2, peaks)
+            also["attn_sweep"] = bench_attention_sweep(d, max(5, args.steps // 2), 3, peaks)
         if args.workload != "lion_c4":
             also["lion_c4"] = bench_lion_c4(d, args.steps, args.warmup, peaks)
         if args.workload != "lion_c5":
