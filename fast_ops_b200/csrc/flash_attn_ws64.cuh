@@ -368,40 +368,8 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     reg_dealloc<80>();
     const int r = (warp & 3) * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    for (int t = 0; t < T1; ++t) {
-#pragma unroll
-      for (int s = 0; s < 2; ++s) {
-        if (t >= (s ? T1 : T0)) continue;
-        mbar_wait(bar_corr + 2 * s + (t & 1), (t >> 1) & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_SOFTMAX);
-        const float alpha = s_alpha[s * 256 + (t & 1) * 128 + r];
-        if (t > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-          // this step's P V is not issued before this warp arrives below; O is complete up to
-          // the previous step once that step's P V has finished.  (The P V of step t - 2 is
-          // known to have finished, since S of step t exists: the phase bit is unambiguous.)
-          mbar_wait(bar_o_full + s, (t - 1) & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_MMA);
-          tcgen05_fence_after_sync();
-          {
-            const uint32_t tO = tmem_base + Cfg::kColO0 + s * D + lane_base;
-#pragma unroll
-            for (int c = 0; c < D / 32; ++c) {
-              uint32_t orr[32];
-              tmem_ld32(tO + c * 32, orr);
-              tmem_ld_wait(orr);
-#pragma unroll
-              for (int i = 0; i < 32; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
-              tmem_st32(tO + c * 32, orr);
-            }
-            tcgen05_wait_st();
-          }
-          tcgen05_fence_before_sync();
-        }
-        mbar_arrive(bar_p_full + 2 * s + (t & 1));
-      }
-    }
-    // epilogue: O / l and LSE
-#pragma unroll
-    for (int s = 0; s < 2; ++s) {
-      const int T_s = s ? T1 : T0;
+    // epilogue of one query tile: O / l and LSE
+    auto epilogue = [&](int s) {
       mbar_wait(bar_final + s, 0, cta_abort, dstat, FO_STATUS_TIMEOUT_SOFTMAX);
       mbar_wait(bar_o_done + s, 0, cta_abort, dstat, FO_STATUS_TIMEOUT_MMA);
       tcgen05_fence_after_sync();
@@ -435,7 +403,42 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         prm.lse[static_cast<int64_t>(bh) * prm.Sq + row] =
             (l_run > 0.f) ? (m_run + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
       }
+    };
+    for (int t = 0; t < T1; ++t) {
+#pragma unroll
+      for (int s = 0; s < 2; ++s) {
+        if (t >= (s ? T1 : T0)) continue;
+        mbar_wait(bar_corr + 2 * s + (t & 1), (t >> 1) & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_SOFTMAX);
+        const float alpha = s_alpha[s * 256 + (t & 1) * 128 + r];
+        if (t > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+          // this step's P V is not issued before this warp arrives below; O is complete up to
+          // the previous step once that step's P V has finished.  (The P V of step t - 2 is
+          // known to have finished, since S of step t exists: the phase bit is unambiguous.)
+          mbar_wait(bar_o_full + s, (t - 1) & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_MMA);
+          tcgen05_fence_after_sync();
+          {
+            const uint32_t tO = tmem_base + Cfg::kColO0 + s * D + lane_base;
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+              uint32_t orr[32];
+              tmem_ld32(tO + c * 32, orr);
+              tmem_ld_wait(orr);
+#pragma unroll
+              for (int i = 0; i < 32; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
+              tmem_st32(tO + c * 32, orr);
+            }
+            tcgen05_wait_st();
+          }
+          tcgen05_fence_before_sync();
+        }
+        mbar_arrive(bar_p_full + 2 * s + (t & 1));
+      }
+      // With a causal mask tile 0 has two steps fewer than tile 1: its epilogue runs here, between
+      // two arrivals for tile 1, instead of at the CTA's tail.
+      if (t == T0 && T0 < T1) epilogue(0);
     }
+    if (T0 == T1) epilogue(0);
+    epilogue(1);
   } else {
     reg_dealloc<48>();
     if (warp == 12 || warp == 14) {

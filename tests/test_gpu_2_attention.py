@@ -70,9 +70,10 @@ def test_attention_matches_oracle(cuda_device, impl, case):
     assert (lse - ref_lse).abs().max().item() <= LSE_TOL
 
 
-def test_long_context_sample_against_oracle(cuda_device, monkeypatch):
+@pytest.mark.parametrize("kernel", ["ws64", "ws"])
+def test_long_context_sample_against_oracle(cuda_device, monkeypatch, kernel):
     """S = 16384, D = 128, bf16, causal (the long-context shape) on two heads, all rows checked."""
-    monkeypatch.setenv("FO_ATTN_IMPL", "ws")
+    monkeypatch.setenv("FO_ATTN_IMPL", kernel)
     q, k, v = attention_inputs(99, 1, 2, 16384, 16384, 128, torch.bfloat16)
     ref, ref_lse = oracle.attention_fwd(q, k, v, causal=True)
     out, lse = run_gpu(q, k, v, cuda_device, causal=True)
@@ -81,8 +82,9 @@ def test_long_context_sample_against_oracle(cuda_device, monkeypatch):
 
 
 def test_full_size_properties(cuda_device, monkeypatch):
-    """B=2, H=32, S=16384, D=128, bf16, causal: properties that need no oracle at this size."""
-    monkeypatch.setenv("FO_ATTN_IMPL", "ws")
+    """B=2, H=32, S=16384, D=128, bf16, causal: properties that need no oracle at this size (the
+    kernel the library chooses by itself)."""
+    monkeypatch.delenv("FO_ATTN_IMPL", raising=False)
     gen = torch.Generator(device=cuda_device).manual_seed(5)
     B, H, S, D = 2, 32, 16384, 128
     q, k, v = (torch.randn(B, H, S, D, generator=gen, device=cuda_device, dtype=torch.float32).bfloat16()
@@ -133,8 +135,12 @@ def test_reference_call_signature_and_errors(cuda_device):
         multi_head_attention(qd.float(), kd.float(), vd.float())
     with pytest.raises(RuntimeError):
         multi_head_attention(q, k, v)  # CPU tensors: no CPU path
+    # a head_dim between the two kernel sizes, as a strided view: runs zero-padded
+    out48 = multi_head_attention(qd[..., :48], kd[..., :48], vd[..., :48])
+    ref48, _ = oracle.attention_fwd(q[..., :48], k[..., :48], v[..., :48])
+    assert (out48.cpu().float() - ref48).abs().max().item() <= TOL[torch.float16]
     with pytest.raises(RuntimeError):
-        multi_head_attention(qd[..., :48], kd[..., :48], vd[..., :48])  # head_dim without a kernel
+        multi_head_attention(qd[..., :44], kd[..., :44], vd[..., :44])  # not a multiple of 8
     with pytest.raises(RuntimeError):
         multi_head_attention(qd, kd[:, :1], vd)
     with pytest.raises(RuntimeError):
