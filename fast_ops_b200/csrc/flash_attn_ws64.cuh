@@ -127,6 +127,25 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   __syncthreads();
   if (*skip) return;  // another CTA already timed out: do nothing
 
+  // The first loads (Q and the first ring fill of K and V) need only the barriers: they go out
+  // here, under the tensor-memory allocation, instead of after it.
+  const int first_fill = min(kStages, 2 * n1);
+  auto load_kv = [&](int i) {  // ring entry i: K_{i/2} (even) or V_{i/2} (odd)
+    const int st = i % kStages;
+    mbar_arrive_expect_tx(bar_kv_full + st, kTileBytes);
+    const CUtensorMap* map = (i & 1) ? &tm_v : &tm_k;
+    for (int c = 0; c < kBoxes; ++c)
+      tma_load_4d(sKV + st * kTileBytes + c * kBoxBytes, map, bar_kv_full + st, c * kBoxCols,
+                  (i >> 1) * kBlockN, hk, b);
+  };
+  if (warp == 13 && lane == 0) {
+    mbar_arrive_expect_tx(bar_q_full, 2 * kTileBytes);
+    for (int s = 0; s < 2; ++s)
+      for (int c = 0; c < kBoxes; ++c)
+        tma_load_4d(sQ + s * kTileBytes + c * kBoxBytes, &tm_q, bar_q_full, c * kBoxCols,
+                    (2 * pair + s) * kBlockM, h, b);
+    for (int i = 0; i < first_fill; ++i) load_kv(i);
+  }
   if (warp == 12) {
     tmem_alloc(tmem_slot, Cfg::kTmemCols);
     tmem_relinquish_alloc_permit();
@@ -543,24 +562,10 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     } else if (warp == 13) {
       // ================================ TMA producer ================================
       const bool issuer = lane == 0;
-      if (issuer) {
-        mbar_arrive_expect_tx(bar_q_full, 2 * kTileBytes);
-        for (int s = 0; s < 2; ++s)
-          for (int c = 0; c < kBoxes; ++c)
-            tma_load_4d(sQ + s * kTileBytes + c * kBoxBytes, &tm_q, bar_q_full, c * kBoxCols,
-                        (2 * pair + s) * kBlockM, h, b);
-      }
-      __syncwarp();
-      for (int i = 0; i < 2 * n1; ++i) {
+      for (int i = first_fill; i < 2 * n1; ++i) {  // the rest of the ring, as slots are released
         const int st = i % kStages;
         mbar_wait(bar_kv_empty + st, ((i / kStages) & 1) ^ 1, cta_abort, dstat, FO_STATUS_TIMEOUT_MMA);
-        if (issuer) {
-          mbar_arrive_expect_tx(bar_kv_full + st, kTileBytes);
-          const CUtensorMap* map = (i & 1) ? &tm_v : &tm_k;
-          for (int c = 0; c < kBoxes; ++c)
-            tma_load_4d(sKV + st * kTileBytes + c * kBoxBytes, map, bar_kv_full + st, c * kBoxCols,
-                        (i >> 1) * kBlockN, hk, b);
-        }
+        if (issuer) load_kv(i);
         __syncwarp();
       }
     }
