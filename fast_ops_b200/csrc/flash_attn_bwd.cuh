@@ -146,6 +146,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   }
   __syncthreads();
   if (*skip) return;
+  // K, V and the first Q / dO need only the barriers: requested here, under the tensor-memory
+  // allocation, instead of after it
+  if (warp == 9 && lane == 0) {
+    mbar_arrive_expect_tx(bar_kv, 2 * kTileBytes);
+    for (int c = 0; c < kBoxes; ++c) tma_load_4d(sK + c * kBoxBytes, &tm_k, bar_kv, c * kBoxCols, k0, h, b);
+    for (int c = 0; c < kBoxes; ++c) tma_load_4d(sV + c * kBoxBytes, &tm_v, bar_kv, c * kBoxCols, k0, h, b);
+    if (n_iter > 0) {
+      const int q0 = i0 * kBlockM;
+      mbar_arrive_expect_tx(bar_q_full, 2 * kTileBytes);
+      for (int c = 0; c < kBoxes; ++c) tma_load_4d(sQ + c * kBoxBytes, &tm_q, bar_q_full, c * kBoxCols, q0, h, b);
+      for (int c = 0; c < kBoxes; ++c) tma_load_4d(sDO + c * kBoxBytes, &tm_do, bar_q_full, c * kBoxCols, q0, h, b);
+    }
+  }
   if (warp == 8) {
     tmem_alloc(tmem_slot, Cfg::kTmemCols);
     tmem_relinquish_alloc_permit();
@@ -436,14 +449,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   } else {
     // ================================ TMA producer ================================
     const bool issuer = lane == 0;
-    if (issuer) {
-      mbar_arrive_expect_tx(bar_kv, 2 * kTileBytes);
-      for (int c = 0; c < kBoxes; ++c) tma_load_4d(sK + c * kBoxBytes, &tm_k, bar_kv, c * kBoxCols, k0, h, b);
-      for (int c = 0; c < kBoxes; ++c) tma_load_4d(sV + c * kBoxBytes, &tm_v, bar_kv, c * kBoxCols, k0, h, b);
-    }
-    __syncwarp();
-    for (int it = 0; it < n_iter; ++it) {
-      if (it > 0) mbar_wait(bar_q_empty, (it - 1) & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_MMA);
+    for (int it = 1; it < n_iter; ++it) {  // tile 0 went out before the allocation
+      mbar_wait(bar_q_empty, (it - 1) & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_MMA);
       if (issuer) {
         const int q0 = (i0 + it) * kBlockM;
         mbar_arrive_expect_tx(bar_q_full, 2 * kTileBytes);
