@@ -597,7 +597,7 @@ def main():
         if not args.workload.startswith("attn_bwd"):
             also["attn_bwd_c3"] = bench_attention_bwd(d, "attn_c3", max(3, args.steps // 4), 2, peaks)
             also["attn_bias_dropout_c3"] = bench_attention_variants(d, "attn_c3", max(3, args.steps // 4), 2, peaks)
-            also["attn_sweep"] = bench_attention_sweep(d, max(5, args.steps // 2), 3, peaks)
+            also["attn_sweep"] = bench_attention_sweep(d, max(10, args.steps // 2), 5, peaks)
         if args.workload != "lion_c4":
             also["lion_c4"] = bench_lion_c4(d, args.steps, args.warmup, peaks)
         if args.workload != "lion_c5":
