@@ -31,6 +31,7 @@ SIGNATURES = {
                                      _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
                                      _I64P, _I64P, _I64P, _I64P,
                                      _c.c_int, _c.c_int, _c.c_float, _c.c_int, _PTR]),
+    "fo_attn_configure": (_c.c_int, [_c.c_int, _c.c_int, _c.c_int]),
     "fo_flash_attn_bwd": (_c.c_int, [_PTR] * 11 + [_c.c_int] * 5 + [_I64P] * 8 +
                           [_c.c_int, _c.c_int, _c.c_float, _c.c_int, _PTR]),
     "fo_flash_attn_fwd_ex": (_c.c_int, [_PTR, _PTR, _PTR, _PTR, _PTR,
@@ -61,6 +62,7 @@ SIGNATURES = {
                                           _c.c_double, _c.c_double, _c.c_double, _c.c_double, _c.c_int, _PTR]),
     "fo_lion_clear_cache": (_c.c_int, []),
     "fo_launch_count": (_c.c_int64, []),
+    "fo_debug_wait_timeout": (_c.c_int, [_c.c_int, _PTR, _c.c_int, _PTR]),
     "fo_debug_set_attn_trace": (_c.c_int, [_PTR]),
     "fo_debug_attn_trace_shape": (_c.c_int, [_c.POINTER(_c.c_int), _c.POINTER(_c.c_int), _c.POINTER(_c.c_int)]),
     "fo_debug_umma_tile": (_c.c_int, [_PTR, _PTR, _PTR, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _PTR]),
@@ -68,7 +70,9 @@ SIGNATURES = {
 
 
 def load() -> ctypes.CDLL:
-    """Returns the loaded library, building it first if the sources are newer (needs nvcc)."""
+    """Returns the loaded library, building it first if the file is missing (needs nvcc).  An
+    existing library is loaded as it is, even when sources are newer: rebuild with
+    `python -m fast_ops_b200.build` after editing them."""
     global _lib
     with _lock:
         if _lib is not None:
@@ -87,8 +91,33 @@ def load() -> ctypes.CDLL:
             fn = getattr(lib, name)  # AttributeError here means header and library disagree
             fn.restype = restype
             fn.argtypes = argtypes
+        _apply_env_options(lib)
         _lib = lib
         return lib
+
+
+ATTN_IMPLS = {"auto": 0, "simple": 1, "ws": 2, "ws64": 3}
+
+
+def attn_configure(impl=None, ping_pong=None, head_group=None) -> None:
+    """Process-wide options of the attention forward (C-ABI fo_attn_configure); None leaves an
+    option unchanged.  impl: "auto" | "simple" | "ws" | "ws64"; ping_pong: bool; head_group: heads
+    scheduled together for L2 reuse, 0 = automatic."""
+    check(load().fo_attn_configure(-1 if impl is None else ATTN_IMPLS[impl],
+                                   -1 if ping_pong is None else int(bool(ping_pong)),
+                                   -1 if head_group is None else int(head_group)))
+
+
+def _apply_env_options(lib) -> None:
+    """FO_ATTN_IMPL / FO_ATTN_PINGPONG / FO_ATTN_HEAD_GROUP are read once, when the library is
+    loaded (the library itself reads no environment variable)."""
+    impl = os.environ.get("FO_ATTN_IMPL")
+    pp = os.environ.get("FO_ATTN_PINGPONG")
+    hg = os.environ.get("FO_ATTN_HEAD_GROUP")
+    if impl is not None and impl not in ATTN_IMPLS:
+        raise RuntimeError(f"FO_ATTN_IMPL must be one of {sorted(ATTN_IMPLS)}, got {impl!r}")
+    lib.fo_attn_configure(-1 if impl is None else ATTN_IMPLS[impl], -1 if pp is None else int(int(pp) != 0),
+                          -1 if hg is None else int(hg))
 
 
 def check(rc: int) -> None:

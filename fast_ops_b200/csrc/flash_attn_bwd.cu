@@ -70,7 +70,7 @@ int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& 
                const CUtensorMap& tdq, const fo::AttnBwdParams& prm, cudaStream_t stream) {
   auto kernel = fo::attn_bwd_kernel<D, kBf16, kExt>;
   constexpr int smem = fo::BwdConfig<D>::kSmemBytes;
-  FO_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  FO_CUDA_CHECK((fo::ensure_dynamic_smem<fo::attn_bwd_kernel<D, kBf16, kExt>>(smem, prm.device)));
   dim3 grid((prm.Sk + fo::kBlockN - 1) / fo::kBlockN, prm.B * prm.H);
   kernel<<<grid, 320, smem, stream>>>(tq, tk, tv, tdo, tdq, prm);
   fo::g_launch_count.fetch_add(1, std::memory_order_relaxed);
@@ -171,6 +171,7 @@ static int attn_bwd_impl(const void* q, const void* k, const void* v, const void
   prm.scale_log2 = softmax_scale * 1.4426950408889634f;
   prm.device_status = status;
   prm.trace = fo::g_attn_trace;
+  prm.device = device;
   std::memset(&prm.ex, 0, sizeof(prm.ex));
   prm.ex.drop_rescale = 1.f;
   const bool ext = ex != nullptr && (ex->bias != nullptr || ex->dropout);

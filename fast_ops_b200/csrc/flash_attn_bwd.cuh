@@ -44,12 +44,17 @@ struct AttnBwdParams {
   float scale_log2;  // scale * log2(e)
   int* device_status;
   unsigned long long* trace;  // optional timeline of CTA (0,0) (debug), or null
+  int device;  // device index of the launch (host side only)
   AttnExtras ex;  // bias / dropout of the forward; read only by the kernel variants built for them
 };
 
 __device__ __forceinline__ void bwd_trace(const AttnBwdParams& prm, int role, int it, int ev) {
+#if FO_ATTN_TRACE
   if (prm.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && (threadIdx.x & 31) == 0 && it < kTraceIters)
     prm.trace[(role * kTraceIters + it) * kTraceEvents + ev] = clock64();
+#else
+  (void)prm; (void)role; (void)it; (void)ev;
+#endif
 }
 
 template <int D>

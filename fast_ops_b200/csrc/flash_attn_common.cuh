@@ -104,6 +104,7 @@ struct AttnParams {
   unsigned long long* trace;
   AttnExtras ex;  // read only by the kernel variants built for bias / dropout
   int ping_pong;  // 64-key-step kernel: the two query tiles take turns on the ex2 units (1) or not (0)
+  int device;     // device index of the launch (host side only)
 };
 
 // One element of a bias row as log2(e) * value; `base` points at column 0 of the row.
@@ -128,9 +129,19 @@ constexpr int kTraceRoles = 3;   // softmax tile 0, softmax tile 1, MMA issuer
 constexpr int kTraceIters = 160;
 constexpr int kTraceEvents = 6;
 
+// The timeline hook is compiled in only with -DFO_ATTN_TRACE=1 (a tuning build): the test of
+// prm.trace sits inside loops whose warps issue in order, so the default build carries none of it.
+#ifndef FO_ATTN_TRACE
+#define FO_ATTN_TRACE 0
+#endif
+
 __device__ __forceinline__ void trace_event(const AttnParams& prm, int role, int j, int ev) {
+#if FO_ATTN_TRACE
   if (prm.trace != nullptr && blockIdx.x == 0 && (threadIdx.x & 31) == 0 && j < kTraceIters)
     prm.trace[(role * kTraceIters + j) * kTraceEvents + ev] = clock64();
+#else
+  (void)prm; (void)role; (void)j; (void)ev;
+#endif
 }
 
 // Descriptor of the kk-th K=16 slice of a K-major [128 x D] tile stored as D/64 boxes.

@@ -18,6 +18,7 @@
 namespace fo {
 // Debug timeline buffer handed to the next attention launches (null = off).
 unsigned long long* g_attn_trace = nullptr;
+AttnOptions g_attn_options;
 }  // namespace fo
 
 namespace {
@@ -127,31 +128,14 @@ umma_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   if (warp == 0) tmem_dealloc(tmem_base, 256);
 }
 
-template <typename Kernel>
-int set_smem(Kernel kernel, int bytes) {
-  FO_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-  return FO_OK;
-}
-
-
-enum class AttnImpl { kAuto, kSimple, kWarpSpecialized, kWarpSpecialized64 };
-
-// FO_ATTN_IMPL=simple|ws|ws64 forces a kernel: the bring-up kernel, the warp-specialised one with
-// 128-key softmax tiles, or the one with 64-key steps.  Unset: chosen per call (below).
-AttnImpl chosen_impl() {
-  const char* e = std::getenv("FO_ATTN_IMPL");
-  if (e && std::strcmp(e, "simple") == 0) return AttnImpl::kSimple;
-  if (e && std::strcmp(e, "ws64") == 0) return AttnImpl::kWarpSpecialized64;
-  if (e && std::strcmp(e, "ws") == 0) return AttnImpl::kWarpSpecialized;
-  return AttnImpl::kAuto;
-}
+enum class AttnImpl { kAuto = 0, kSimple = 1, kWarpSpecialized = 2, kWarpSpecialized64 = 3 };
 
 template <int D, bool kBf16>
 int launch_simple(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& prm,
                   cudaStream_t stream) {
   auto kernel = fo::attn_fwd_simple_kernel<D, kBf16>;
   constexpr int smem = fo::simple_smem_bytes<D>();
-  if (int rc = set_smem(kernel, smem)) return rc;
+  FO_CUDA_CHECK((fo::ensure_dynamic_smem<fo::attn_fwd_simple_kernel<D, kBf16>>(smem, prm.device)));
   dim3 grid(prm.num_q_tiles, prm.B * prm.H);
   kernel<<<grid, 128, smem, stream>>>(tq, tk, tv, prm);
   fo::g_launch_count.fetch_add(1, std::memory_order_relaxed);
@@ -251,10 +235,8 @@ static int attn_fwd_impl(const void* q, const void* k, const void* v, void* o, f
   prm.num_q_tiles = (Sq + kBlockM - 1) / kBlockM;
   prm.trace = g_attn_trace;
   prm.kv_head_bcast = kv_bcast ? 1 : 0;
-  {
-    const char* e = std::getenv("FO_ATTN_PINGPONG");
-    prm.ping_pong = (e && std::atoi(e) == 0) ? 0 : 1;
-  }
+  prm.ping_pong = fo::g_attn_options.ping_pong.load(std::memory_order_relaxed);
+  prm.device = device;
   std::memset(&prm.ex, 0, sizeof(prm.ex));
   prm.ex.drop_rescale = 1.f;
   const bool ext = ex != nullptr && (ex->bias != nullptr || ex->dropout);
@@ -264,8 +246,8 @@ static int attn_fwd_impl(const void* q, const void* k, const void* v, void* o, f
     // third of the 126 MB L2, leaving room for Q, O and the other traffic
     const int64_t kv_bytes = 4LL * Sk * D;
     int64_t g = (40LL << 20) / kv_bytes;
-    const char* e = std::getenv("FO_ATTN_HEAD_GROUP");
-    if (e) g = std::atoi(e);
+    const int forced = fo::g_attn_options.head_group.load(std::memory_order_relaxed);
+    if (forced > 0) g = forced;
     if (g < 1) g = 1;
     if (g > static_cast<int64_t>(B) * H) g = static_cast<int64_t>(B) * H;
     prm.head_group = static_cast<int>(g);
@@ -273,7 +255,7 @@ static int attn_fwd_impl(const void* q, const void* k, const void* v, void* o, f
 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool bf16 = dtype == FO_BF16;
-  AttnImpl impl = chosen_impl();
+  AttnImpl impl = static_cast<AttnImpl>(fo::g_attn_options.impl.load(std::memory_order_relaxed));
   if (impl == AttnImpl::kAuto) {
     // The 64-key-step kernel is the faster one at every shape measured (same box, hot loop, bf16
     // causal: S=16384 1.11 against 1.02 PFLOP/s, S=4096 0.98 against 0.82, GPT-2-small shape
@@ -385,10 +367,10 @@ extern "C" int fo_debug_umma_tile(const void* a, const void* b, float* c, int N,
   const int smem = 4 * fo::kBoxBytes + 1024 + 128;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == FO_BF16) {
-    if (int rc = set_smem(umma_tile_kernel<true>, smem)) return rc;
+    FO_CUDA_CHECK((fo::ensure_dynamic_smem<umma_tile_kernel<true>>(smem, device)));
     umma_tile_kernel<true><<<1, 128, smem, s>>>(ta, tb, static_cast<const uint16_t*>(a), c, N, K, mode, status);
   } else {
-    if (int rc = set_smem(umma_tile_kernel<false>, smem)) return rc;
+    FO_CUDA_CHECK((fo::ensure_dynamic_smem<umma_tile_kernel<false>>(smem, device)));
     umma_tile_kernel<false><<<1, 128, smem, s>>>(ta, tb, static_cast<const uint16_t*>(a), c, N, K, mode, status);
   }
   fo::g_launch_count.fetch_add(1, std::memory_order_relaxed);
@@ -396,9 +378,57 @@ extern "C" int fo_debug_umma_tile(const void* a, const void* b, float* c, int N,
   return FO_OK;
 }
 
+// One warp waits, through the kernels' bounded wait, on a barrier that nobody arrives on.
+__global__ void wait_timeout_kernel(int* device_status, unsigned long long budget_ns, int* returned) {
+  using namespace fo;
+  __shared__ uint64_t bar;
+  __shared__ int abort_word;
+  volatile int* cta_abort = &abort_word;
+  if (threadIdx.x == 0) {
+    *cta_abort = 0;
+    mbar_init(&bar, 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+  const bool ok = mbar_wait_budget(&bar, 0, cta_abort, device_status, FO_STATUS_TIMEOUT_SELFTEST, budget_ns);
+  __syncthreads();
+  if (threadIdx.x == 0 && returned != nullptr) *returned = ok ? 1 : 2;  // 2: gave up and came back
+}
+
+extern "C" int fo_debug_wait_timeout(int budget_us, int* returned, int device, void* stream) {
+  fo::clear_error();
+  FO_REQUIRE(budget_us >= 1 && budget_us <= 100000, "budget_us must be in [1, 100000] (got %d)", budget_us);
+  fo::DeviceGuard guard(device);
+  FO_REQUIRE(guard.ok, "cannot make device %d current", device);
+  int* status = fo::device_status_ptr(device);
+  if (!status) return fo::fail(FO_ERR_CUDA, "cannot resolve the status word of device %d", device);
+  wait_timeout_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      status, static_cast<unsigned long long>(budget_us) * 1000ull, returned);
+  fo::g_launch_count.fetch_add(1, std::memory_order_relaxed);
+  FO_CUDA_CHECK(cudaGetLastError());
+  return FO_OK;
+}
+
+extern "C" int fo_attn_configure(int impl, int ping_pong, int head_group) {
+  fo::clear_error();
+  FO_REQUIRE(impl >= -1 && impl <= 3, "impl must be -1 (keep), 0 (auto), 1 (simple), 2 (128-key) or 3 (64-key)");
+  FO_REQUIRE(ping_pong >= -1 && ping_pong <= 1, "ping_pong must be -1 (keep), 0 or 1");
+  FO_REQUIRE(head_group >= -1, "head_group must be -1 (keep), 0 (automatic) or a positive head count");
+  if (impl >= 0) fo::g_attn_options.impl.store(impl, std::memory_order_relaxed);
+  if (ping_pong >= 0) fo::g_attn_options.ping_pong.store(ping_pong, std::memory_order_relaxed);
+  if (head_group >= 0) fo::g_attn_options.head_group.store(head_group, std::memory_order_relaxed);
+  return FO_OK;
+}
+
 extern "C" int fo_debug_set_attn_trace(void* device_buffer) {
+  fo::clear_error();
+#if FO_ATTN_TRACE
   g_attn_trace = static_cast<unsigned long long*>(device_buffer);
   return FO_OK;
+#else
+  if (device_buffer == nullptr) return FO_OK;
+  return fo::fail(FO_ERR_UNSUPPORTED, "this build has no timeline hook: rebuild with -DFO_ATTN_TRACE=1");
+#endif
 }
 
 extern "C" int fo_debug_attn_trace_shape(int* roles, int* iters, int* events) {

@@ -23,11 +23,6 @@
 
 namespace fo {
 
-// 1: overlap each tensor-memory load of S with the row maximum of the previous chunk.
-#ifndef FO_WS_PIPE_LD
-#define FO_WS_PIPE_LD 1
-#endif
-
 template <int D>
 struct WsConfig {
   static constexpr int kTileBytes = kBlockM * D * 2;
@@ -219,23 +214,14 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       const bool need_mask = (k0 + kBlockN > prm.Sk) || (prm.causal && k0 + kBlockN - 1 > q0);
       uint32_t sr[4][32];
       float mxa = -INFINITY, mxb = -INFINITY, mxc = -INFINITY, mxd = -INFINITY;
-#if FO_WS_PIPE_LD == 1
       // Tensor-memory loads are software-pipelined against the row maximum: chunk c+1 is in
       // flight while chunk c is reduced.
       tmem_ld32(tS, sr[0]);
       tmem_ld_wait(sr[0]);
       if ((warp & 3) == 0) trace_event(prm, s, j, 4);
-#else
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, sr[c]);
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld_wait(sr[c]);
-#endif
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-#if FO_WS_PIPE_LD == 1
         if (c + 1 < 4) tmem_ld32(tS + (c + 1) * 32, sr[c + 1]);
-#endif
         if constexpr (kExt) {
           if (vec_bias) {
             const float4* bv = reinterpret_cast<const float4*>(sb + (j & 1) * 128 + c * 32);
@@ -270,9 +256,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           mxc = max3(mxc, __uint_as_float(sr[c][i + 4]), __uint_as_float(sr[c][i + 5]));
           mxd = max3(mxd, __uint_as_float(sr[c][i + 6]), __uint_as_float(sr[c][i + 7]));
         }
-#if FO_WS_PIPE_LD == 1
         if (c + 1 < 4) tmem_ld_wait(sr[c + 1]);
-#endif
       }
       const float mx = fmaxf(fmaxf(mxa, mxb), fmaxf(mxc, mxd));
       if ((warp & 3) == 0) trace_event(prm, s, j, 5);
@@ -517,8 +501,7 @@ int launch_ws(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& t
               cudaStream_t stream) {
   auto kernel = attn_fwd_ws_kernel<D, kBf16, kExt>;
   constexpr int smem = WsConfig<D>::kSmemBytes;
-  // The attribute is per device; setting it again is cheap and keeps multi-device callers right.
-  cudaError_t ea = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  cudaError_t ea = ensure_dynamic_smem<attn_fwd_ws_kernel<D, kBf16, kExt>>(smem, prm.device);
   if (ea != cudaSuccess)
     return fail(FO_ERR_CUDA, "cudaFuncSetAttribute(shared memory %d) failed: %s", smem, cudaGetErrorString(ea));
   const int num_pairs = (prm.num_q_tiles + 1) / 2;

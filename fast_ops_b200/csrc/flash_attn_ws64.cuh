@@ -581,7 +581,7 @@ int launch_ws64(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap&
                 cudaStream_t stream) {
   auto kernel = attn_fwd_ws64_kernel<D, kBf16, kExt>;
   constexpr int smem = Ws64Config<D>::kSmemBytes;
-  cudaError_t ea = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  cudaError_t ea = ensure_dynamic_smem<attn_fwd_ws64_kernel<D, kBf16, kExt>>(smem, prm.device);
   if (ea != cudaSuccess)
     return fail(FO_ERR_CUDA, "cudaFuncSetAttribute(shared memory %d) failed: %s", smem, cudaGetErrorString(ea));
   const int num_pairs = (prm.num_q_tiles + 1) / 2;

@@ -26,6 +26,26 @@ extern std::atomic<int64_t> g_launch_count;
 // Device buffer for the attention kernels' debug timeline (fo_debug_set_attn_trace), or null.
 extern unsigned long long* g_attn_trace;
 
+// Options of the attention forward that fo_attn_configure sets (process-wide; -1 / 0 = default).
+struct AttnOptions {
+  std::atomic<int> impl{0};        // 0 chosen per call, 1 simple, 2 128-key kernel, 3 64-key kernel
+  std::atomic<int> ping_pong{1};   // 64-key kernel: the two query tiles alternate on the ex2 units
+  std::atomic<int> head_group{0};  // heads scheduled together for L2 reuse; 0 = from the K/V size
+};
+extern AttnOptions g_attn_options;
+
+// Raises a kernel's dynamic shared-memory limit once per device (the attribute is per device and
+// per kernel).  The kernel is a template argument, so that every kernel has once-flags of its own.
+template <auto kKernel>
+inline cudaError_t ensure_dynamic_smem(int bytes, int device) {
+  static std::atomic<uint64_t> done{0};  // bit d: set on device d (devices >= 64 set it every time)
+  const uint64_t bit = (device >= 0 && device < 64) ? (1ull << device) : 0;
+  if (bit && (done.load(std::memory_order_acquire) & bit)) return cudaSuccess;
+  cudaError_t e = cudaFuncSetAttribute(kKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess && bit) done.fetch_or(bit, std::memory_order_release);
+  return e;
+}
+
 // RAII: make `device` current for the scope, restore the previous one afterwards.
 struct DeviceGuard {
   int prev = -1;
@@ -62,3 +82,4 @@ struct DeviceGuard {
 #define FO_STATUS_TIMEOUT_MMA 0x2    // a wait for a tcgen05.commit gave up
 #define FO_STATUS_TIMEOUT_SOFTMAX 0x4  // a wait on a softmax/correction hand-off gave up
 #define FO_STATUS_TIMEOUT_EPILOGUE 0x8
+#define FO_STATUS_TIMEOUT_SELFTEST 0x10  // the wait of fo_debug_wait_timeout gave up (as it must)

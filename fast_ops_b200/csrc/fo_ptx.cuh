@@ -80,8 +80,8 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
 // the host sees the status word.
 constexpr uint64_t kWaitBudgetNs = 1000ull * 1000ull * 1000ull;  // 1 s
 
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* cta_abort,
-                                          int* device_status, int code) {
+__device__ __forceinline__ bool mbar_wait_budget(uint64_t* bar, uint32_t parity, volatile int* cta_abort,
+                                                 int* device_status, int code, uint64_t budget_ns) {
   // the common case first: a completed phase costs one try_wait and no shared-memory load
   if (mbar_try_wait(bar, parity)) return true;
   if (*cta_abort) return false;
@@ -90,7 +90,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 0x3ff) == 0) {
       if (*cta_abort) return false;
-      if (global_timer_ns() - t0 > kWaitBudgetNs) {
+      if (global_timer_ns() - t0 > budget_ns) {
         *cta_abort = code;
         atomicOr(device_status, code);
         return false;
@@ -98,6 +98,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     }
   }
   return true;
+}
+
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* cta_abort,
+                                          int* device_status, int code) {
+  return mbar_wait_budget(bar, parity, cta_abort, device_status, code, kWaitBudgetNs);
 }
 
 // ---- TMA ------------------------------------------------------------------------------------

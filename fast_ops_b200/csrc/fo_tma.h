@@ -33,8 +33,8 @@ inline EncodeTiledFn encode_fn() {
 // Tensor map over a (B, H, S, D) tensor with element strides (sb, sh, ss, 1): dimensions are
 // listed innermost first, the box is one [128 rows x 64 columns] swizzled tile, and reads
 // past S are filled with zeros.
-inline int make_tensor_map(CUtensorMap* map, const void* base, int dtype, int B, int H, int S, int D,
-                    const int64_t strides[3], const char* name) {
+inline int encode_tensor_map(CUtensorMap* map, const void* base, int dtype, int B, int H, int S, int D,
+                             const int64_t strides[3], const char* name) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return fo::fail(FO_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   FO_REQUIRE((reinterpret_cast<uintptr_t>(base) & 15) == 0, "%s must be 16-byte aligned", name);
@@ -54,6 +54,46 @@ inline int make_tensor_map(CUtensorMap* map, const void* base, int dtype, int B,
   CUresult r = fn(map, dt, 4, const_cast<void*>(base), dims, gstrides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fo::fail(FO_ERR_CUDA, "cuTensorMapEncodeTiled(%s) failed with CUresult %d", name, (int)r);
+  return FO_OK;
+}
+
+// The same through a small per-thread cache: a tensor map depends only on the base address, the
+// element type and the geometry, never on the tensor's contents, and a training or serving loop
+// presents the same few (address, shape, strides) combinations call after call.  A hit costs a
+// scan of at most kTensorMapCacheSize keys instead of a driver call.
+constexpr int kTensorMapCacheSize = 16;
+
+struct TensorMapKey {
+  const void* base;
+  int64_t strides[3];
+  int dtype, B, H, S, D;
+  bool operator==(const TensorMapKey& o) const {
+    return base == o.base && strides[0] == o.strides[0] && strides[1] == o.strides[1] && strides[2] == o.strides[2] &&
+           dtype == o.dtype && B == o.B && H == o.H && S == o.S && D == o.D;
+  }
+};
+
+struct TensorMapCache {
+  TensorMapKey keys[kTensorMapCacheSize];
+  alignas(64) CUtensorMap maps[kTensorMapCacheSize];
+  int used = 0, next = 0;  // entries in use; slot the next miss overwrites (round robin)
+};
+
+inline int make_tensor_map(CUtensorMap* map, const void* base, int dtype, int B, int H, int S, int D,
+                           const int64_t strides[3], const char* name) {
+  thread_local TensorMapCache cache;
+  const TensorMapKey key{base, {strides[0], strides[1], strides[2]}, dtype, B, H, S, D};
+  for (int i = 0; i < cache.used; ++i)
+    if (cache.keys[i] == key) {
+      *map = cache.maps[i];
+      return FO_OK;
+    }
+  if (int rc = encode_tensor_map(map, base, dtype, B, H, S, D, strides, name)) return rc;
+  const int slot = cache.next;
+  cache.keys[slot] = key;
+  cache.maps[slot] = *map;
+  cache.next = (slot + 1) % kTensorMapCacheSize;
+  if (cache.used < kTensorMapCacheSize) ++cache.used;
   return FO_OK;
 }
 

@@ -24,6 +24,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <atomic>
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -34,21 +35,9 @@
 
 namespace {
 
-#ifndef FO_LION_THREADS
-#define FO_LION_THREADS 256
-#endif
-#ifndef FO_LION_UNROLL
-#define FO_LION_UNROLL 4
-#endif
-#ifndef FO_LION_CTAS_PER_SM
-#define FO_LION_CTAS_PER_SM 0  // 0: ask the occupancy calculator
-#endif
-#ifndef FO_LION_STREAMING
-#define FO_LION_STREAMING 1  // 1: ld.global.cs / st.global.cs (evict-first), 0: default cache policy
-#endif
-constexpr int kThreads = FO_LION_THREADS;
+constexpr int kThreads = 256;
 constexpr int kVec = 8;     // elements per thread per group (16 B of a 16-bit type)
-constexpr int kUnroll = FO_LION_UNROLL;  // groups per thread per chunk
+constexpr int kUnroll = 4;  // groups per thread per chunk
 constexpr int kChunk = kThreads * kVec * kUnroll;  // 8192 elements
 
 struct LionTensor {
@@ -103,11 +92,7 @@ __device__ __forceinline__ void load_group(Group<T>& dst, const T* src) {
   const uint4* s = reinterpret_cast<const uint4*>(src);
   uint4* d = reinterpret_cast<uint4*>(dst.v);
 #pragma unroll
-#if FO_LION_STREAMING
-  for (int i = 0; i < n16; ++i) d[i] = __ldcs(s + i);
-#else
-  for (int i = 0; i < n16; ++i) d[i] = s[i];
-#endif
+  for (int i = 0; i < n16; ++i) d[i] = __ldcs(s + i);  // streaming: every byte is touched once
 }
 
 template <typename T>
@@ -116,11 +101,7 @@ __device__ __forceinline__ void store_group(T* dst, const Group<T>& src) {
   uint4* d = reinterpret_cast<uint4*>(dst);
   const uint4* s = reinterpret_cast<const uint4*>(src.v);
 #pragma unroll
-#if FO_LION_STREAMING
   for (int i = 0; i < n16; ++i) __stcs(d + i, s[i]);
-#else
-  for (int i = 0; i < n16; ++i) d[i] = s[i];
-#endif
 }
 
 template <typename TP, typename TM>
@@ -140,6 +121,103 @@ __device__ __forceinline__ void lion_element(TP& p_io, TP g_in, TM& m_io, const 
   m_io = Elem<TM>::store(__fmaf_rn(c.c_1mb2, g, m1));
 }
 
+// The same arithmetic on two neighbouring elements at once: packed fp32 pairs (mul/add/fma.f32x2)
+// and two-at-a-time conversions halve the instruction count, which matters for all-16-bit
+// tensors (eight elements per 16-byte vector: the scalar form issues about 25 instructions per
+// 10 bytes of traffic).  Every packed operation rounds each half exactly like its scalar form.
+//
+// One shortcut: the sum t1 + t2 is not rounded to the promoted type before its sign is taken.
+// t1 and t2 are values of that type, so a non-zero sum is at least the type's smallest
+// subnormal in magnitude and cannot round to zero (nor change sign); NaN gives sign 0 either way.
+template <typename T> struct Pair;
+template <> struct Pair<float> {
+  using Packed = float2;
+  static __device__ __forceinline__ float2 load(float2 x) { return x; }
+  static __device__ __forceinline__ float2 round(float2 x) { return x; }
+  static __device__ __forceinline__ float2 store(float2 x) { return x; }
+};
+template <> struct Pair<__nv_bfloat16> {
+  using Packed = __nv_bfloat162;
+  static __device__ __forceinline__ float2 load(__nv_bfloat162 x) { return __bfloat1622float2(x); }
+  static __device__ __forceinline__ float2 round(float2 x) { return __bfloat1622float2(__float22bfloat162_rn(x)); }
+  static __device__ __forceinline__ __nv_bfloat162 store(float2 x) { return __float22bfloat162_rn(x); }
+};
+template <> struct Pair<__half> {
+  using Packed = __half2;
+  static __device__ __forceinline__ float2 load(__half2 x) { return __half22float2(x); }
+  static __device__ __forceinline__ float2 round(float2 x) { return __half22float2(__float22half2_rn(x)); }
+  static __device__ __forceinline__ __half2 store(float2 x) { return __float22half2_rn(x); }
+};
+
+__device__ __forceinline__ float sign3(float u) { return (u > 0.f) ? 1.f : ((u < 0.f) ? -1.f : 0.f); }
+
+template <typename TP, typename TM>
+__device__ __forceinline__ void lion_pair(typename Pair<TP>::Packed& p_io, typename Pair<TP>::Packed g_in,
+                                          typename Pair<TM>::Packed& m_io, const LionConsts& c) {
+  const float2 p = Pair<TP>::load(p_io);
+  const float2 g = Pair<TP>::load(g_in);
+  const float2 m = Pair<TM>::load(m_io);
+  const float2 p1 = Pair<TP>::round(__fmul2_rn(p, make_float2(c.c_wd, c.c_wd)));
+  const float2 t1 = Pair<TM>::round(__fmul2_rn(m, make_float2(c.c_b1, c.c_b1)));
+  const float2 t2 = Pair<TP>::round(__fmul2_rn(g, make_float2(c.c_1mb1, c.c_1mb1)));
+  const float2 u = __fadd2_rn(t1, t2);
+  const float2 s = make_float2(sign3(u.x), sign3(u.y));
+  p_io = Pair<TP>::store(__ffma2_rn(make_float2(c.c_nlr, c.c_nlr), s, p1));
+  const float2 m1 = Pair<TM>::round(__fmul2_rn(m, make_float2(c.c_b2, c.c_b2)));
+  m_io = Pair<TM>::store(__ffma2_rn(make_float2(c.c_1mb2, c.c_1mb2), g, m1));
+}
+
+// One 16-byte-vector group of kVec elements.
+template <typename TP, typename TM>
+__device__ __forceinline__ void lion_group(Group<TP>& pv, const Group<TP>& gv, Group<TM>& mv, const LionConsts& c) {
+  using PP = typename Pair<TP>::Packed;
+  using PM = typename Pair<TM>::Packed;
+  PP* p2 = reinterpret_cast<PP*>(pv.v);
+  const PP* g2 = reinterpret_cast<const PP*>(gv.v);
+  PM* m2 = reinterpret_cast<PM*>(mv.v);
+#pragma unroll
+  for (int i = 0; i < kVec / 2; ++i) lion_pair<TP, TM>(p2[i], g2[i], m2[i], c);
+}
+
+// One chunk: `remaining` elements are left from p, g, m on (kChunk of them are this chunk's
+// unless the tensor ends earlier); `aligned` says that all three addresses allow 16-byte accesses.
+template <typename TP, typename TM>
+__device__ __forceinline__ void lion_chunk(TP* p, const TP* g, TM* m, int64_t remaining, bool aligned,
+                                           const LionConsts& c) {
+  if (aligned && remaining >= kChunk) {
+    Group<TP> pv[kUnroll], gv[kUnroll];
+    Group<TM> mv[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int off = (u * kThreads + threadIdx.x) * kVec;
+      load_group(pv[u], p + off);
+      load_group(gv[u], g + off);
+      load_group(mv[u], m + off);
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      lion_group<TP, TM>(pv[u], gv[u], mv[u], c);
+      const int off = (u * kThreads + threadIdx.x) * kVec;
+      store_group(p + off, pv[u]);
+      store_group(m + off, mv[u]);
+    }
+  } else {
+    // Ragged tail of a tensor, or a tensor whose storage is not 16-byte aligned.
+    const int n = remaining < kChunk ? static_cast<int>(remaining) : kChunk;
+    for (int i = threadIdx.x; i < n; i += kThreads) {
+      TP pe = p[i];
+      TM me = m[i];
+      lion_element<TP, TM>(pe, g[i], me, c);
+      p[i] = pe;
+      m[i] = me;
+    }
+  }
+}
+
+__device__ __forceinline__ bool all_aligned16(const void* a, const void* b, const void* c) {
+  return ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c)) & 15) == 0;
+}
+
 // One launch covers all tensors.  `chunk_start[t]` is the index of tensor t's first
 // chunk in the global chunk numbering (chunk_start[n_tensors] = total).  CTAs stride
 // over chunks; because a CTA's chunk index only grows, it finds the owning tensor by
@@ -153,8 +231,7 @@ lion_multi_tensor_kernel(const LionTensor* __restrict__ tensors,
   int64_t t_first = 0;            // chunk_start[t]
   int64_t t_end = __ldg(chunk_start + 1);  // chunk_start[t + 1]
   LionTensor cur = tensors[0];
-  bool aligned = ((reinterpret_cast<uintptr_t>(cur.p) | reinterpret_cast<uintptr_t>(cur.g) |
-                   reinterpret_cast<uintptr_t>(cur.m)) & 15) == 0;
+  bool aligned = all_aligned16(cur.p, cur.g, cur.m);
 
   for (int64_t chunk = blockIdx.x; chunk < total_chunks; chunk += gridDim.x) {
     if (chunk >= t_end) {
@@ -164,44 +241,25 @@ lion_multi_tensor_kernel(const LionTensor* __restrict__ tensors,
       } while (chunk >= t_end && t + 1 < n_tensors);
       t_first = __ldg(chunk_start + t);
       cur = tensors[t];
-      aligned = ((reinterpret_cast<uintptr_t>(cur.p) | reinterpret_cast<uintptr_t>(cur.g) |
-                  reinterpret_cast<uintptr_t>(cur.m)) & 15) == 0;
+      aligned = all_aligned16(cur.p, cur.g, cur.m);
     }
     const int64_t base = (chunk - t_first) * kChunk;
-    const int64_t remaining = cur.numel - base;
-    TP* p = static_cast<TP*>(cur.p) + base;
-    const TP* g = static_cast<const TP*>(cur.g) + base;
-    TM* m = static_cast<TM*>(cur.m) + base;
+    lion_chunk<TP, TM>(static_cast<TP*>(cur.p) + base, static_cast<const TP*>(cur.g) + base,
+                       static_cast<TM*>(cur.m) + base, cur.numel - base, aligned, c);
+  }
+}
 
-    if (aligned && remaining >= kChunk) {
-      Group<TP> pv[kUnroll], gv[kUnroll];
-      Group<TM> mv[kUnroll];
-#pragma unroll
-      for (int u = 0; u < kUnroll; ++u) {
-        const int off = (u * kThreads + threadIdx.x) * kVec;
-        load_group(pv[u], p + off);
-        load_group(gv[u], g + off);
-        load_group(mv[u], m + off);
-      }
-#pragma unroll
-      for (int u = 0; u < kUnroll; ++u) {
-#pragma unroll
-        for (int i = 0; i < kVec; ++i) lion_element<TP, TM>(pv[u].v[i], gv[u].v[i], mv[u].v[i], c);
-        const int off = (u * kThreads + threadIdx.x) * kVec;
-        store_group(p + off, pv[u]);
-        store_group(m + off, mv[u]);
-      }
-    } else {
-      // Ragged tail of a tensor, or a tensor whose storage is not 16-byte aligned.
-      const int n = remaining < kChunk ? static_cast<int>(remaining) : kChunk;
-      for (int i = threadIdx.x; i < n; i += kThreads) {
-        TP pe = p[i];
-        TM me = m[i];
-        lion_element<TP, TM>(pe, g[i], me, c);
-        p[i] = pe;
-        m[i] = me;
-      }
-    }
+// The same step on ONE tensor, described by the kernel's own arguments: no device table, so
+// nothing is allocated, copied or cached for it (the per-tensor call of the reference's
+// optimizer loop, and a ZeRO-1 shard, come through here).
+template <typename TP, typename TM>
+__global__ void __launch_bounds__(kThreads)
+lion_single_tensor_kernel(TP* __restrict__ p, const TP* __restrict__ g, TM* __restrict__ m, int64_t numel,
+                          int64_t total_chunks, LionConsts c) {
+  const bool aligned = all_aligned16(p, g, m);
+  for (int64_t chunk = blockIdx.x; chunk < total_chunks; chunk += gridDim.x) {
+    const int64_t base = chunk * kChunk;
+    lion_chunk<TP, TM>(p + base, g + base, m + base, numel - base, aligned, c);
   }
 }
 
@@ -212,27 +270,42 @@ struct Plan {
   int n_tensors = 0;
   int64_t total_chunks = 0;
   void* d_blob = nullptr;  // [LionTensor x n][int64 x (n+1)]
+  uint64_t last_use = 0;   // value of g_plan_clock at the latest call with this list
 };
 
 std::mutex g_plan_mutex;
 std::map<std::string, Plan> g_plans;  // key: device + raw bytes of the tensor list
+uint64_t g_plan_clock = 0;
 
 constexpr size_t kMaxPlans = 32;
 
 // cudaFree waits for the device's pending work, so a table still in use by a kernel
-// in flight is not released under it.
-void drop_all_plans_locked() {
+// in flight is not released under it.  A CUDA graph that captured a launch keeps the
+// table's address: dropping the table invalidates that graph.
+void free_plan_locked(Plan& plan) {
+  if (!plan.d_blob) return;
   int prev = -1;
   cudaGetDevice(&prev);
-  for (auto& kv : g_plans) {
-    if (kv.second.d_blob) {
-      cudaSetDevice(kv.second.device);
-      cudaDeviceSynchronize();
-      cudaFree(kv.second.d_blob);
-    }
-  }
-  g_plans.clear();
+  cudaSetDevice(plan.device);
+  cudaDeviceSynchronize();
+  cudaFree(plan.d_blob);
+  plan.d_blob = nullptr;
   if (prev >= 0) cudaSetDevice(prev);
+}
+
+void drop_all_plans_locked() {
+  for (auto& kv : g_plans) free_plan_locked(kv.second);
+  g_plans.clear();
+}
+
+// Makes room for one more list by dropping the one that has gone unused the longest.
+void evict_oldest_plan_locked() {
+  auto oldest = g_plans.begin();
+  for (auto it = g_plans.begin(); it != g_plans.end(); ++it)
+    if (it->second.last_use < oldest->second.last_use) oldest = it;
+  if (oldest == g_plans.end()) return;
+  free_plan_locked(oldest->second);
+  g_plans.erase(oldest);
 }
 
 int sm_count(int device) {
@@ -267,20 +340,27 @@ int make_consts(double lr, double beta1, double beta2, double wd, int p_dtype, i
   return FO_OK;
 }
 
+// Size of the persistent grid: exactly one resident wave, as many CTAs per SM as the kernel's
+// register use allows (a partial second wave costs up to 20 %), never more CTAs than chunks.
+// The occupancy query is made once per kernel instantiation.
+template <auto kKernel>
+int64_t one_wave_grid(int device, int64_t total_chunks) {
+  static std::atomic<int> cached_per_sm{0};  // one per kernel: the kernel is a template argument
+  int per_sm = cached_per_sm.load(std::memory_order_relaxed);
+  if (per_sm == 0) {
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kKernel, kThreads, 0) != cudaSuccess || per_sm < 1)
+      per_sm = 4;
+    cached_per_sm.store(per_sm, std::memory_order_relaxed);
+  }
+  const int64_t grid = static_cast<int64_t>(sm_count(device)) * per_sm;
+  return grid > total_chunks ? total_chunks : grid;
+}
+
 template <typename TP, typename TM>
 int launch_typed(const Plan& plan, const LionConsts& c, cudaStream_t stream) {
   const LionTensor* tensors = static_cast<const LionTensor*>(plan.d_blob);
   const int64_t* chunk_start = reinterpret_cast<const int64_t*>(tensors + plan.n_tensors);
-  // Persistent grid of exactly one resident wave: as many CTAs per SM as the kernel's register
-  // use allows, each striding over the chunks (a partial second wave costs up to 20 %).
-  int per_sm = FO_LION_CTAS_PER_SM;
-  if (per_sm == 0) {
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, lion_multi_tensor_kernel<TP, TM>, kThreads, 0) !=
-            cudaSuccess || per_sm < 1)
-      per_sm = 4;
-  }
-  int64_t grid = static_cast<int64_t>(sm_count(plan.device)) * per_sm;
-  if (grid > plan.total_chunks) grid = plan.total_chunks;
+  const int64_t grid = one_wave_grid<lion_multi_tensor_kernel<TP, TM>>(plan.device, plan.total_chunks);
   lion_multi_tensor_kernel<TP, TM><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
       tensors, chunk_start, plan.n_tensors, plan.total_chunks, c);
   fo::g_launch_count.fetch_add(1, std::memory_order_relaxed);
@@ -288,19 +368,43 @@ int launch_typed(const Plan& plan, const LionConsts& c, cudaStream_t stream) {
   return FO_OK;
 }
 
+template <typename TP, typename TM>
+int launch_single_typed(void* p, const void* g, void* m, int64_t numel, const LionConsts& c, int device,
+                        cudaStream_t stream) {
+  const int64_t total_chunks = (numel + kChunk - 1) / kChunk;
+  const int64_t grid = one_wave_grid<lion_single_tensor_kernel<TP, TM>>(device, total_chunks);
+  lion_single_tensor_kernel<TP, TM><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
+      static_cast<TP*>(p), static_cast<const TP*>(g), static_cast<TM*>(m), numel, total_chunks, c);
+  fo::g_launch_count.fetch_add(1, std::memory_order_relaxed);
+  FO_CUDA_CHECK(cudaGetLastError());
+  return FO_OK;
+}
+
+#define FO_LION_DTYPE_CASES(CASE)                      \
+  CASE(FO_BF16, FO_BF16, __nv_bfloat16, __nv_bfloat16) \
+  CASE(FO_BF16, FO_F32, __nv_bfloat16, float)          \
+  CASE(FO_BF16, FO_F16, __nv_bfloat16, __half)         \
+  CASE(FO_F16, FO_F16, __half, __half)                 \
+  CASE(FO_F16, FO_F32, __half, float)                  \
+  CASE(FO_F16, FO_BF16, __half, __nv_bfloat16)         \
+  CASE(FO_F32, FO_F32, float, float)                   \
+  CASE(FO_F32, FO_BF16, float, __nv_bfloat16)          \
+  CASE(FO_F32, FO_F16, float, __half)
+
 int launch(const Plan& plan, int p_dtype, int m_dtype, const LionConsts& c, cudaStream_t stream) {
   if (plan.total_chunks == 0) return FO_OK;
 #define FO_LION_CASE(PD, MD, TP, TM) \
   if (p_dtype == PD && m_dtype == MD) return launch_typed<TP, TM>(plan, c, stream);
-  FO_LION_CASE(FO_BF16, FO_BF16, __nv_bfloat16, __nv_bfloat16)
-  FO_LION_CASE(FO_BF16, FO_F32, __nv_bfloat16, float)
-  FO_LION_CASE(FO_BF16, FO_F16, __nv_bfloat16, __half)
-  FO_LION_CASE(FO_F16, FO_F16, __half, __half)
-  FO_LION_CASE(FO_F16, FO_F32, __half, float)
-  FO_LION_CASE(FO_F16, FO_BF16, __half, __nv_bfloat16)
-  FO_LION_CASE(FO_F32, FO_F32, float, float)
-  FO_LION_CASE(FO_F32, FO_BF16, float, __nv_bfloat16)
-  FO_LION_CASE(FO_F32, FO_F16, float, __half)
+  FO_LION_DTYPE_CASES(FO_LION_CASE)
+#undef FO_LION_CASE
+  return fo::fail(FO_ERR_INVALID_ARGUMENT, "unsupported Lion dtype combination p=%d m=%d", p_dtype, m_dtype);
+}
+
+int launch_single(void* p, const void* g, void* m, int64_t numel, int p_dtype, int m_dtype, const LionConsts& c,
+                  int device, cudaStream_t stream) {
+#define FO_LION_CASE(PD, MD, TP, TM) \
+  if (p_dtype == PD && m_dtype == MD) return launch_single_typed<TP, TM>(p, g, m, numel, c, device, stream);
+  FO_LION_DTYPE_CASES(FO_LION_CASE)
 #undef FO_LION_CASE
   return fo::fail(FO_ERR_INVALID_ARGUMENT, "unsupported Lion dtype combination p=%d m=%d", p_dtype, m_dtype);
 }
@@ -360,35 +464,46 @@ extern "C" int fo_lion_multi_tensor_step(void* const* params, const void* const*
 
   fo::DeviceGuard guard(device);
   FO_REQUIRE(guard.ok, "cannot make device %d current", device);
+  if (n == 1)  // no table needed: the tensor travels in the kernel's arguments
+    return launch_single(ps[0], gs[0], ms[0], ns[0], p_dtype, m_dtype, c, device, static_cast<cudaStream_t>(stream));
 
   std::vector<char> blob;
   const int64_t total = build_table(ps.data(), gs.data(), ms.data(), ns.data(), n, &blob);
   std::string key(reinterpret_cast<const char*>(&device), sizeof(device));
   key.append(blob.data(), blob.size());
 
-  Plan plan;
-  {
-    std::lock_guard<std::mutex> lock(g_plan_mutex);
-    auto it = g_plans.find(key);
-    if (it == g_plans.end()) {
-      // A caller whose pointers change every step would grow the cache without bound.
-      if (g_plans.size() >= kMaxPlans) drop_all_plans_locked();
-      plan.device = device;
-      plan.n_tensors = n;
-      plan.total_chunks = total;
-      FO_CUDA_CHECK(cudaMalloc(&plan.d_blob, blob.size()));
-      // Synchronous copy: the host image dies with this call, and the table is built once.
-      cudaError_t e = cudaMemcpy(plan.d_blob, blob.data(), blob.size(), cudaMemcpyHostToDevice);
-      if (e != cudaSuccess) {
-        cudaFree(plan.d_blob);
-        return fo::fail(FO_ERR_CUDA, "tensor table upload failed: %s", cudaGetErrorString(e));
-      }
-      g_plans.emplace(std::move(key), plan);
-    } else {
-      plan = it->second;
+  // The lock is held across the launch: a table can then not be evicted (by another thread's
+  // new list) between the lookup and the moment its kernel is in the stream, and cudaFree does
+  // not release memory under a kernel that is already there.
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  std::lock_guard<std::mutex> lock(g_plan_mutex);
+  auto it = g_plans.find(key);
+  if (it == g_plans.end()) {
+    cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+    FO_CUDA_CHECK(cudaStreamIsCapturing(s, &capture));
+    if (capture != cudaStreamCaptureStatusNone)
+      return fo::fail(FO_ERR_UNSUPPORTED,
+                      "first call with this tensor list on a capturing stream: call once outside the capture so "
+                      "that the device table exists");
+    // A caller whose pointers change every step would grow the cache without bound.
+    if (g_plans.size() >= kMaxPlans) evict_oldest_plan_locked();
+    Plan plan;
+    plan.device = device;
+    plan.n_tensors = n;
+    plan.total_chunks = total;
+    FO_CUDA_CHECK(cudaMalloc(&plan.d_blob, blob.size()));
+    // On the caller's stream, so that the copy and the kernel below are ordered whatever kind of
+    // stream it is.  The source is pageable: the runtime has staged it when the call returns,
+    // so the host image may die with this call.
+    cudaError_t e = cudaMemcpyAsync(plan.d_blob, blob.data(), blob.size(), cudaMemcpyHostToDevice, s);
+    if (e != cudaSuccess) {
+      cudaFree(plan.d_blob);
+      return fo::fail(FO_ERR_CUDA, "tensor table upload failed: %s", cudaGetErrorString(e));
     }
+    it = g_plans.emplace(std::move(key), plan).first;
   }
-  return launch(plan, p_dtype, m_dtype, c, static_cast<cudaStream_t>(stream));
+  it->second.last_use = ++g_plan_clock;
+  return launch(it->second, p_dtype, m_dtype, c, s);
 }
 
 extern "C" int fo_lion_clear_cache(void) {
@@ -402,12 +517,16 @@ extern "C" int fo_lion_update(void* param, const void* grad, void* exp_avg, int6
                               int p_dtype, int g_dtype, int m_dtype,
                               double lr, double beta1, double beta2, double weight_decay,
                               int device, void* stream) {
-  void* ps[1] = {param};
-  const void* gs[1] = {grad};
-  void* ms[1] = {exp_avg};
-  int64_t ns[1] = {numel};
-  return fo_lion_multi_tensor_step(ps, gs, ms, ns, 1, p_dtype, g_dtype, m_dtype, lr, beta1, beta2,
-                                   weight_decay, device, stream);
+  fo::clear_error();
+  if (int rc = check_dtypes(p_dtype, g_dtype, m_dtype)) return rc;
+  FO_REQUIRE(numel >= 0, "negative numel");
+  if (numel == 0) return FO_OK;
+  FO_REQUIRE(param && grad && exp_avg, "null pointer");
+  LionConsts c;
+  if (int rc = make_consts(lr, beta1, beta2, weight_decay, p_dtype, m_dtype, &c)) return rc;
+  fo::DeviceGuard guard(device);
+  FO_REQUIRE(guard.ok, "cannot make device %d current", device);
+  return launch_single(param, grad, exp_avg, numel, p_dtype, m_dtype, c, device, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int fo_lion_flat_step(void* param, const void* grad, void* exp_avg_shard,
@@ -452,8 +571,11 @@ static __device__ __align__(256) unsigned char g_noalloc_table[kNoAllocTableByte
 constexpr int kNoAllocMaxDevices = 64;
 std::mutex g_noalloc_mutex;
 void* g_noalloc_dev_ptr[kNoAllocMaxDevices] = {};  // device address of g_noalloc_table, per device
-// Host image of the table; guarded by g_noalloc_mutex.  cudaMemcpyAsync from pageable memory has
-// taken its copy of the source by the time it returns, so the image can be reused by the next call.
+// Host image of the table; guarded by g_noalloc_mutex.  Outside stream capture cudaMemcpyAsync
+// from pageable memory has taken its copy of the source by the time it returns, so the image can
+// be reused by the next call.  Inside a capture the copy would become a graph node that reads this
+// shared image at every replay (by then it holds whatever list came last), so a capturing stream
+// is refused.
 alignas(16) unsigned char g_noalloc_host[kNoAllocTableBytes];
 
 }  // namespace
@@ -480,6 +602,14 @@ extern "C" int fo_lion_multi_tensor_step_noalloc(void* const* params, const void
   fo::DeviceGuard guard(device);
   FO_REQUIRE(guard.ok, "cannot make device %d current", device);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  {
+    cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+    FO_CUDA_CHECK(cudaStreamIsCapturing(s, &capture));
+    if (capture != cudaStreamCaptureStatusNone)
+      return fo::fail(FO_ERR_UNSUPPORTED,
+                      "the allocation-free Lion step cannot run on a capturing stream: its table upload would read "
+                      "the shared host image at replay time");
+  }
 
   std::lock_guard<std::mutex> lock(g_noalloc_mutex);
   if (g_noalloc_dev_ptr[device] == nullptr) {
@@ -551,8 +681,14 @@ lion_flat_push_kernel(TP* __restrict__ p_local, const TP* __restrict__ g, TM* __
   // p_local, g and the peers' bases address element 0 of the flat buffers; m_shard addresses the
   // momentum of element `begin`.
   const int64_t total_chunks = (numel + kChunk - 1) / kChunk;
-  const bool aligned = ((reinterpret_cast<uintptr_t>(p_local + begin) | reinterpret_cast<uintptr_t>(g + begin) |
-                         reinterpret_cast<uintptr_t>(m_shard)) & 15) == 0;
+  // 16-byte accesses need every address aligned, the peers' included (their buffers may start
+  // anywhere an element may); one unaligned buffer sends the whole shard down the scalar path
+  uintptr_t addr_bits = reinterpret_cast<uintptr_t>(p_local + begin) | reinterpret_cast<uintptr_t>(g + begin) |
+                        reinterpret_cast<uintptr_t>(m_shard);
+#pragma unroll
+  for (int r = 0; r < kMaxPeers; ++r)
+    if (r < peers.n) addr_bits |= reinterpret_cast<uintptr_t>(static_cast<TP*>(peers.base[r]) + begin);
+  const bool aligned = (addr_bits & 15) == 0;
   for (int64_t chunk = blockIdx.x; chunk < total_chunks; chunk += gridDim.x) {
     const int64_t base = chunk * kChunk;
     const int64_t remaining = numel - base;
@@ -571,8 +707,7 @@ lion_flat_push_kernel(TP* __restrict__ p_local, const TP* __restrict__ g, TM* __
       }
 #pragma unroll
       for (int u = 0; u < kUnroll; ++u) {
-#pragma unroll
-        for (int i = 0; i < kVec; ++i) lion_element<TP, TM>(pv[u].v[i], gv[u].v[i], mv[u].v[i], c);
+        lion_group<TP, TM>(pv[u], gv[u], mv[u], c);
         const int off = (u * kThreads + threadIdx.x) * kVec;
         store_group(p + off, pv[u]);
         store_group(m + off, mv[u]);
@@ -607,14 +742,7 @@ template <typename TP, typename TM>
 int launch_push(void* p, const void* g, void* m, int64_t begin, int64_t numel, const PeerList& peers,
                 const LionConsts& c, int device, cudaStream_t stream) {
   const int64_t total_chunks = (numel + kChunk - 1) / kChunk;
-  int per_sm = FO_LION_CTAS_PER_SM;
-  if (per_sm == 0) {
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, lion_flat_push_kernel<TP, TM>, kThreads, 0) !=
-            cudaSuccess || per_sm < 1)
-      per_sm = 4;
-  }
-  int64_t grid = static_cast<int64_t>(sm_count(device)) * per_sm;
-  if (grid > total_chunks) grid = total_chunks;
+  const int64_t grid = one_wave_grid<lion_flat_push_kernel<TP, TM>>(device, total_chunks);
   lion_flat_push_kernel<TP, TM><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
       static_cast<TP*>(p), static_cast<const TP*>(g), static_cast<TM*>(m), begin, numel, peers, c);
   fo::g_launch_count.fetch_add(1, std::memory_order_relaxed);

@@ -219,17 +219,25 @@ def flash_attention_backward(dO: Tensor, Q: Tensor, K: Tensor, V: Tensor, O: Ten
 
 
 class _AttentionFunction(Function):
-    """Forward + backward with the keyword arguments carried as non-tensor inputs."""
+    """Forward + backward with the keyword arguments carried as non-tensor inputs.
+
+    `rng` is the (seed, offset) pair of the dropout mask, or None to draw it from the device's
+    generator when `dropout_p` > 0; with `bshd_out` O is allocated as a (B, S, H, D) block and
+    returned as its (B, H, S, D) view, so that the caller's transpose back is contiguous."""
 
     @staticmethod
     def forward(ctx, Q: Tensor, K: Tensor, V: Tensor, causal: bool, softmax_scale: Optional[float],
-                bias: Optional[Tensor], dropout_p: float):
-        rng = None
-        if dropout_p > 0.0:
+                bias: Optional[Tensor], dropout_p: float, rng: Optional[Tuple[int, int]] = None,
+                bshd_out: bool = False):
+        if rng is None and dropout_p > 0.0:
             # one index per attention probability (flash_attention_triton.py:780)
             rng = next_dropout_rng(Q.device, Q.shape[0] * Q.shape[1] * Q.shape[2] * K.shape[2])
+        out = None
+        if bshd_out:
+            B, H, M, D = Q.shape
+            out = torch.empty((B, M, H, D), dtype=Q.dtype, device=Q.device).transpose(1, 2)
         O, lse = flash_attention_forward(Q, K, V, causal=causal, softmax_scale=softmax_scale, return_lse=True,
-                                         bias=bias, dropout_p=dropout_p, rng=rng)
+                                         bias=bias, dropout_p=dropout_p, rng=rng, out=out)
         ctx.save_for_backward(Q, K, V, O, lse, bias)
         ctx.causal, ctx.softmax_scale, ctx.dropout_p, ctx.rng = causal, softmax_scale, dropout_p, rng
         ctx.mark_non_differentiable(lse)
@@ -245,7 +253,7 @@ class _AttentionFunction(Function):
         dQ, dK, dV = flash_attention_backward(dO, Q, K, V, O, lse, causal=ctx.causal,
                                               softmax_scale=ctx.softmax_scale, bias=bias,
                                               dropout_p=ctx.dropout_p, rng=ctx.rng)
-        return dQ, dK, dV, None, None, None, None
+        return dQ, dK, dV, None, None, None, None, None, None
 
 
 class FlashAttentionFunction(Function):

@@ -18,16 +18,18 @@ from .flash_attention import _AttentionFunction, dropout_mask, flash_attention_f
 def flash_attn_bshd(q: Tensor, k: Tensor, v: Tensor, bias: Optional[Tensor] = None, causal: bool = False,
                     dropout_p: float = 0.0, softmax_scale: Optional[float] = None) -> Tensor:
     """q: (B, Sq, H, D); k, v: (B, Sk, H, D); bias broadcastable to (B, H, Sq, Sk) with last two
-    dimensions (1, Sk) or (Sq, Sk).  Returns (B, Sq, H, D) in q's dtype.  With `dropout_p` > 0 the
-    mask comes from the device's default generator, which is advanced as the reference does."""
+    dimensions (1, Sk) or (Sq, Sk).  Returns a contiguous (B, Sq, H, D) tensor in q's dtype.  The
+    dropout mask comes from the device's default generator, which every call advances by one index
+    per attention probability, with or without dropout, as the reference does."""
     qt, kt, vt = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
+    # The reference advances the generator on every forward, dropout or not
+    # (flash_attention_triton.py:780), so the offsets of later draws agree with a reference run.
+    rng = next_dropout_rng(q.device, q.shape[0] * q.shape[2] * q.shape[1] * k.shape[1])
+    # O has q's layout in both paths, as in the reference (flash_attention_triton.py:773)
     if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad):
-        o, _ = _AttentionFunction.apply(qt, kt, vt, bool(causal), softmax_scale, bias, float(dropout_p))
-        return o.transpose(1, 2)
-    rng = None
-    if dropout_p > 0.0:
-        rng = next_dropout_rng(q.device, q.shape[0] * q.shape[2] * q.shape[1] * k.shape[1])
-    o = torch.empty_like(q)  # the reference allocates O with q's layout (flash_attention_triton.py:773)
+        ot, _ = _AttentionFunction.apply(qt, kt, vt, bool(causal), softmax_scale, bias, float(dropout_p), rng, True)
+        return ot.transpose(1, 2)
+    o = torch.empty((q.shape[0], q.shape[1], q.shape[2], q.shape[3]), dtype=q.dtype, device=q.device)
     flash_attention_forward(qt, kt, vt, causal=causal, softmax_scale=softmax_scale, out=o.transpose(1, 2),
                             bias=bias, dropout_p=float(dropout_p), rng=rng)
     return o

@@ -73,6 +73,18 @@ int fo_flash_attn_fwd(const void* q, const void* k, const void* v, void* o, floa
                       int device, void* stream);
 
 /*
+ * Process-wide options of the attention forward (tuning and tests; nothing in the reference
+ * corresponds).  Each argument: -1 leaves the option as it is.
+ *   impl       : 0 = chosen per call (default), 1 = the unoverlapped bring-up kernel, 2 = the
+ *                warp-specialised kernel with 128-key softmax tiles, 3 = the one with 64-key steps.
+ *   ping_pong  : 64-key kernel: 1 (default) = the two query tiles of a CTA take turns on the
+ *                exponential units, 0 = they run free.
+ *   head_group : heads scheduled together so that their K and V stay in L2; 0 (default) = derived
+ *                from the K/V size.
+ */
+int fo_attn_configure(int impl, int ping_pong, int head_group);
+
+/*
  * FlashAttention backward: dQ, dK, dV for the output gradient `dout`, given the forward's inputs,
  * its output O and its LSE.  The reference's CUDA path leaves backward unimplemented
  * (fast_ops/flash_attention/flash_attention.py:41-45); the semantics are those of its complete
@@ -215,7 +227,10 @@ int fo_lion_flat_step_push(void* param, const void* grad, void* exp_avg_shard,
  *   - At most 1024 tensors per call; a longer list is rejected with FO_ERR_INVALID_ARGUMENT
  *     (split it, or use fo_lion_multi_tensor_step).
  *   - It calls no cudaMalloc, cudaFree or other allocating routine.  The first call on a device
- *     looks up the array's device address; make that first call outside any stream capture.
+ *     looks up the array's device address.
+ *   - A stream that is being captured is refused with FO_ERR_UNSUPPORTED: the table upload would
+ *     turn into a graph node that reads the library's one host-side image at replay time, when it
+ *     holds the list of whichever call came last.
  *   - The table is copied to the device on `stream` on every call, ahead of the kernel.  All
  *     calls on a device share the one array and every call rewrites the entries it uses:
  *     calls on the same stream are ordered, but two calls whose kernels can overlap on the GPU
@@ -248,10 +263,22 @@ int fo_debug_umma_tile(const void* a, const void* b, float* c, int N, int K,
                        int dtype, int mode, int device, void* stream);
 
 /*
- * Kernel-tuning aid: after fo_debug_set_attn_trace(buf) the warp-specialised attention kernel
- * records, for its first CTA, SM clock values of the hand-offs between its softmax warps and its
- * MMA issuer into `buf` (device memory of roles*iters*events 64-bit words, see
- * fo_debug_attn_trace_shape; zero it first).  Pass NULL to switch the recording off.
+ * Self-test of the bounded device-side wait that every attention kernel uses: launches one warp
+ * that waits, with a budget of `budget_us` microseconds (1 .. 100000), on a barrier nobody will
+ * ever arrive on.  The wait must give up, OR FO_STATUS bit 0x10 into the device status word
+ * (fo_device_status then reports it until reset) and the kernel must return normally; `returned`
+ * (device int, may be NULL) receives 2 when that happened.  No fault is involved at any point.
+ * Test use only; nothing in the reference corresponds.
+ */
+int fo_debug_wait_timeout(int budget_us, int* returned, int device, void* stream);
+
+/*
+ * Kernel-tuning aid, present only in a library built with -DFO_ATTN_TRACE=1 (the default build
+ * returns FO_ERR_UNSUPPORTED for a non-NULL buffer): after fo_debug_set_attn_trace(buf) the
+ * warp-specialised attention kernels record, for their first CTA, SM clock values of the
+ * hand-offs between the softmax warps and the MMA issuer into `buf` (device memory of
+ * roles*iters*events 64-bit words, see fo_debug_attn_trace_shape; zero it first).  NULL switches
+ * the recording off.
  */
 int fo_debug_set_attn_trace(void* device_buffer);
 int fo_debug_attn_trace_shape(int* roles, int* iters, int* events);

@@ -232,7 +232,10 @@ def make_lion(LionRef):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <path of the jfc4050/fast-ops checkout> [all|attention|attention_bwd|"
+                         "attention_ex|lion]")
+    ref_root = sys.argv[1]
     os.environ["TRITON_INTERPRET"] = "1"  # the reference's mask kernel runs on the CPU
     sys.path.insert(0, ref_root)
     from fast_ops.flash_attention.attention_ref import attention_ref

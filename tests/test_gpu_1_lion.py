@@ -179,3 +179,111 @@ def test_lion_step_replays_from_a_cuda_graph(cuda_device):
             oracle.lion_step(cp, g, cm, 1e-3, (0.9, 0.99), 0.1)
     for p, cp, cm in zip(params, cpu_p, cpu_m):
         assert torch.equal(p.detach().cpu(), cp) and torch.equal(opt.state[p]["exp_avg"].cpu(), cm)
+
+
+def _gpt2_medium_shapes():
+    """The GPT-2-medium parameter list of the fused-Lion benchmark configuration: 290 tensors,
+    354 821 120 parameters (wte, wpe, 24 blocks of 4 weight/bias pairs and 2 LayerNorm pairs)."""
+    shapes = [(50257, 1024), (1024, 1024)]
+    for _ in range(24):
+        shapes += [(1024, 3072), (3072,), (1024, 1024), (1024,), (1024, 4096), (4096,), (4096, 1024), (1024,),
+                   (1024,), (1024,), (1024,), (1024,)]
+    return shapes
+
+
+def test_lion_full_gpt2_medium_list_bit_exact(cuda_device):
+    """The whole 290-tensor list in one launch per step (43 313 chunks, a 51 M-element first tensor,
+    many 1024-element vectors that fill an eighth of a chunk), fp32 p/g with bf16 momentum, the
+    benchmark's hyper-parameters, three steps, every element compared with the oracle."""
+    gen = torch.Generator().manual_seed(355)
+    shapes = _gpt2_medium_shapes()
+    assert len(shapes) == 290 and sum(int(np.prod(s)) for s in shapes) == 354_821_120
+    cpu_p = [torch.randn(s, generator=gen) * 0.02 for s in shapes]
+    cpu_m = [torch.zeros(s, dtype=torch.bfloat16) for s in shapes]
+    params = [t.clone().to(cuda_device).requires_grad_(True) for t in cpu_p]
+    lr, betas, wd = 1e-4, (0.9, 0.99), 0.1
+    opt = Lion(params, lr=lr, betas=betas, weight_decay=wd, momentum_dtype=torch.bfloat16)
+    launches0 = L.load().fo_launch_count()
+    for step in range(3):
+        grads = [torch.randn(s, generator=gen) * 1e-3 for s in shapes]
+        for p, g in zip(params, grads):
+            p.grad = g.to(cuda_device)
+        opt.step()
+        for cp, g, cm in zip(cpu_p, grads, cpu_m):
+            oracle.lion_step(cp, g, cm, lr, betas, wd)
+    assert L.load().fo_launch_count() - launches0 == 3
+    for i, (p, cp, cm) in enumerate(zip(params, cpu_p, cpu_m)):
+        assert torch.equal(p.detach().cpu(), cp), f"param {i} {shapes[i]} differs from the oracle"
+        assert torch.equal(opt.state[p]["exp_avg"].cpu(), cm), f"exp_avg {i} {shapes[i]} differs from the oracle"
+    assert L.device_status(cuda_device.index) == 0
+
+
+def test_lion_flat_step_on_the_last_shard_of_a_llama7b_sized_buffer(cuda_device):
+    """ZeRO-1 shard 7 of 8 of a flat bf16 buffer of 6 738 411 520 elements: `begin` lies beyond
+    2^31 elements (and beyond 2^32 bytes), which the small flat-range tests never reach.  Windows of
+    2^20 elements at the shard's start, middle and end are compared with the oracle; the elements
+    just outside the shard must stay untouched."""
+    free, _ = torch.cuda.mem_get_info(cuda_device)
+    total = 6_738_411_520
+    if free < 2 * 2 * total + (8 << 30):
+        pytest.skip("needs about 30 GB of free device memory")
+    assert total % 64 == 0
+    shard = total // 8
+    begin, end = 7 * shard, total
+    assert begin > 2 ** 31
+    flat_p = torch.empty(total, device=cuda_device, dtype=torch.bfloat16)
+    flat_g = torch.empty(total, device=cuda_device, dtype=torch.bfloat16)
+    gen = torch.Generator(device=cuda_device).manual_seed(70)
+    # only the shard and a margin before it need defined values
+    lo = begin - (1 << 20)
+    piece = 1 << 27
+    for off in range(lo, total, piece):
+        n = min(piece, total - off)
+        flat_p[off:off + n] = (torch.randn(n, generator=gen, device=cuda_device) * 0.02).bfloat16()
+        flat_g[off:off + n] = (torch.randn(n, generator=gen, device=cuda_device) * 1e-3).bfloat16()
+    m_shard = (torch.randn(shard, generator=gen, device=cuda_device) * 1e-3).bfloat16()
+    w = 1 << 20
+    windows = [begin, begin + (shard // 2) // 8 * 8 + 3, end - w]  # one of them off the 16-byte grid
+    before = [(flat_p[a:a + w].cpu(), flat_g[a:a + w].cpu(), m_shard[a - begin:a - begin + w].cpu()) for a in windows]
+    margin = flat_p[lo:begin].clone()
+    lib = L.load()
+    hyper = (3e-5, 0.9, 0.99, 0.1)
+    L.check(lib.fo_lion_flat_step(flat_p.data_ptr(), flat_g.data_ptr(), m_shard.data_ptr(), begin, end, L.FO_BF16,
+                                  L.FO_BF16, L.FO_BF16, *hyper, cuda_device.index, L.current_stream_ptr(cuda_device)))
+    torch.cuda.synchronize()
+    for a, (p0, g0, m0) in zip(windows, before):
+        oracle.lion_step(p0, g0, m0, hyper[0], (hyper[1], hyper[2]), hyper[3])
+        assert torch.equal(flat_p[a:a + w].cpu(), p0), f"window at {a}: parameters differ from the oracle"
+        assert torch.equal(m_shard[a - begin:a - begin + w].cpu(), m0), f"window at {a}: momentum differs"
+    assert torch.equal(flat_p[lo:begin], margin), "elements before the shard were modified"
+    assert L.device_status(cuda_device.index) == 0
+
+
+@pytest.mark.parametrize("peer_offset", [0, 1], ids=["aligned_peer", "unaligned_peer"])
+def test_flat_step_push_takes_any_peer_alignment(cuda_device, peer_offset):
+    """fo_lion_flat_step_push with a second buffer of the same device standing in for a peer: the
+    updated slice lands in both buffers, also when the peer's buffer starts off the 16-byte grid
+    (the 16-byte stores are then not usable; the kernel must fall back, not fault)."""
+    import ctypes
+
+    n, begin, end = 40000, 8192, 8192 + 24576 + 5
+    gen = torch.Generator().manual_seed(17)
+    p0 = (torch.randn(n, generator=gen) * 0.02).bfloat16()
+    g = (torch.randn(n, generator=gen) * 1e-3).bfloat16()
+    m0 = (torch.randn(end - begin, generator=gen) * 1e-3).bfloat16()
+    local = p0.clone().to(cuda_device)
+    peer_store = torch.zeros(n + 8, device=cuda_device, dtype=torch.bfloat16)
+    peer = peer_store[peer_offset:peer_offset + n]
+    m = m0.clone().to(cuda_device)
+    lib = L.load()
+    arr = (ctypes.c_void_p * 1)(peer.data_ptr())
+    L.check(lib.fo_lion_flat_step_push(local.data_ptr(), g.to(cuda_device).data_ptr(), m.data_ptr(), begin, end, arr, 1,
+                                       L.FO_BF16, L.FO_BF16, L.FO_BF16, 1e-3, 0.9, 0.99, 0.1, cuda_device.index,
+                                       L.current_stream_ptr(cuda_device)))
+    torch.cuda.synchronize()
+    want_p, want_m = p0[begin:end].clone(), m0.clone()
+    oracle.lion_step(want_p, g[begin:end].clone(), want_m, 1e-3, (0.9, 0.99), 0.1)
+    assert torch.equal(local[begin:end].cpu(), want_p) and torch.equal(m.cpu(), want_m)
+    assert torch.equal(peer[begin:end].cpu(), want_p), "the peer's copy of the slice differs"
+    assert torch.count_nonzero(peer[:begin]) == 0 and torch.count_nonzero(peer[end:]) == 0
+    assert torch.equal(local[:begin].cpu(), p0[:begin]) and torch.equal(local[end:].cpu(), p0[end:])

@@ -20,9 +20,10 @@ IMPLS = ["ws", "ws64", "simple"]
 
 
 @pytest.fixture(params=IMPLS)
-def impl(request, monkeypatch):
-    monkeypatch.setenv("FO_ATTN_IMPL", request.param)
-    return request.param
+def impl(request):
+    L.attn_configure(impl=request.param)
+    yield request.param
+    L.attn_configure(impl="auto")
 
 
 def run_gpu(q, k, v, device, **kw):
@@ -71,20 +72,23 @@ def test_attention_matches_oracle(cuda_device, impl, case):
 
 
 @pytest.mark.parametrize("kernel", ["ws64", "ws"])
-def test_long_context_sample_against_oracle(cuda_device, monkeypatch, kernel):
+def test_long_context_sample_against_oracle(cuda_device, kernel):
     """S = 16384, D = 128, bf16, causal (the long-context shape) on two heads, all rows checked."""
-    monkeypatch.setenv("FO_ATTN_IMPL", kernel)
+    L.attn_configure(impl=kernel)
     q, k, v = attention_inputs(99, 1, 2, 16384, 16384, 128, torch.bfloat16)
     ref, ref_lse = oracle.attention_fwd(q, k, v, causal=True)
-    out, lse = run_gpu(q, k, v, cuda_device, causal=True)
+    try:
+        out, lse = run_gpu(q, k, v, cuda_device, causal=True)
+    finally:
+        L.attn_configure(impl="auto")
     assert (out.float() - ref).abs().max().item() <= TOL[torch.bfloat16]
     assert (lse - ref_lse).abs().max().item() <= LSE_TOL
 
 
-def test_full_size_properties(cuda_device, monkeypatch):
+def test_full_size_properties(cuda_device):
     """B=2, H=32, S=16384, D=128, bf16, causal: properties that need no oracle at this size (the
     kernel the library chooses by itself)."""
-    monkeypatch.delenv("FO_ATTN_IMPL", raising=False)
+    L.attn_configure(impl="auto")
     gen = torch.Generator(device=cuda_device).manual_seed(5)
     B, H, S, D = 2, 32, 16384, 128
     q, k, v = (torch.randn(B, H, S, D, generator=gen, device=cuda_device, dtype=torch.float32).bfloat16()
@@ -106,8 +110,11 @@ def test_full_size_properties(cuda_device, monkeypatch):
     # rows are convex combinations of V rows
     assert o1.float().abs().max() <= v.float().abs().max() * 1.01
     # the two kernels agree on a slice
-    monkeypatch.setenv("FO_ATTN_IMPL", "simple")
-    os_, ls_ = flash_attention_forward(q[:1, :2], k[:1, :2], v[:1, :2], causal=True, return_lse=True)
+    L.attn_configure(impl="simple")
+    try:
+        os_, ls_ = flash_attention_forward(q[:1, :2], k[:1, :2], v[:1, :2], causal=True, return_lse=True)
+    finally:
+        L.attn_configure(impl="auto")
     assert (os_.float() - o1[:1, :2].float()).abs().max().item() <= 1e-2
     assert (ls_ - l1[:1, :2]).abs().max().item() <= 1e-3
 

@@ -45,7 +45,9 @@ def _worker(rank, world, port, fused, reduce, ret):
         for step in range(3):
             grads = [(torch.randn(s, generator=gen) * 1e-3).bfloat16() for s in shapes]
             for p, g in zip(params, grads):
-                # with reduce_gradients the ranks hold g/2 and 3g/2, whose average is g exactly
+                # with reduce_gradients the ranks hold g/2 and 3g/2 (3g/2 rounded to bf16): the average need
+                # not be g bit for bit, but it has g's sign and Lion's parameter update uses only that;
+                # the momentum is therefore not compared in this mode
                 p.grad.copy_((g * (1.0 if not reduce else (0.5 if rank == 0 else 1.5))).to(dev))
             opt.step()
             for rp, g, rm in zip(ref_p, grads, ref_m):

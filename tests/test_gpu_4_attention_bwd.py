@@ -119,3 +119,63 @@ def test_backward_other_head_dims(cuda_device, D):
     want = oracle.attention_bwd(q, k, v, dout, causal=True)
     got, same = run_backward(q, k, v, dout, True, cuda_device)
     check(got, same, want, f"D={D}")
+
+
+def _bwd_ex(device, q, k, v, dout, causal, bias=None, p=0.0, rng=None):
+    """Forward + backward with optional bias / dropout; returns (grads, same-precision torch grads, keep mask)."""
+    from fast_ops_b200.flash_attention import dropout_mask
+
+    qd, kd, vd, dd = (t.to(device) for t in (q, k, v, dout))
+    bd = None if bias is None else bias.to(device)
+    o, lse = flash_attention_forward(qd, kd, vd, causal=causal, return_lse=True, bias=bd, dropout_p=p, rng=rng)
+    got = flash_attention_backward(dd, qd, kd, vd, o, lse, causal=causal, bias=bd, dropout_p=p, rng=rng)
+    torch.cuda.synchronize()
+    assert L.device_status(device.index) == 0, "a kernel wait timed out"
+    keep = dropout_mask(p, q.shape[0], q.shape[1], q.shape[2], k.shape[2], device, rng=rng) if p > 0 else None
+    # same-precision torch with the same bias and mask (tests/test_flash_attention_triton.py:107-117)
+    qs, ks, vs = (t.clone().requires_grad_(True) for t in (qd, kd, vd))
+    d = q.shape[-1]
+    scores = torch.matmul(qs, (ks / d ** 0.5).transpose(-1, -2))
+    if bd is not None:
+        scores = (scores + bd).to(scores.dtype)
+    if causal:
+        mask = torch.triu(torch.ones(q.shape[2], k.shape[2], dtype=torch.bool, device=device), 1)
+        scores = scores.masked_fill(mask, float("-inf"))
+    attn = torch.softmax(scores, dim=-1)
+    if keep is not None:
+        attn = attn.masked_fill(~keep, 0.0)
+    torch.matmul(attn, vs * (1.0 / (1.0 - p))).backward(dd)
+    return got, (qs.grad, ks.grad, vs.grad), keep
+
+
+@pytest.mark.parametrize("variant", ["plain", "vector_bias", "dropout"])
+def test_backward_at_32_key_tiles(cuda_device, variant):
+    """S = 4096, D = 128, bf16, causal: every query tile's dQ is the sum of up to 32 bulk
+    reduce-adds from different CTAs (the small cases above stop at 8)."""
+    B, H, S, D = 1, 2, 4096, 128
+    q, k, v = attention_inputs(4096, B, H, S, S, D, torch.bfloat16)
+    dout = attention_dout(4097, B, H, S, D, torch.bfloat16)
+    bias, p, rng = None, 0.0, None
+    if variant == "vector_bias":
+        bias = torch.randn(1, H, 1, S, generator=torch.Generator().manual_seed(4098))
+        bias[..., 5::23] = float("-inf")
+    if variant == "dropout":
+        p, rng = 0.17, (0, 16773120 + 4096 - (B * H * S * S) // 2 // 4 * 4)
+    got, same, keep = _bwd_ex(cuda_device, q, k, v, dout, True, bias, p, rng)
+    keep_cpu = None
+    if p > 0:
+        keep_cpu = oracle.dropout_mask(p, B, H, S, S, *rng)
+        assert torch.equal(keep.cpu(), keep_cpu)
+    want = oracle.attention_ex(q, k, v, bias=bias, keep_mask=keep_cpu, dropout_p=p, causal=True, dout=dout)
+    check(got, same, want[2:], f"S=4096 {variant}")
+
+
+def test_backward_at_the_long_context_length(cuda_device):
+    """One head at S = 16384, D = 128, bf16, causal: the depth the benchmark times (128 key tiles;
+    dQ of the last query tile is accumulated from 128 CTAs)."""
+    B, H, S, D = 1, 1, 16384, 128
+    q, k, v = attention_inputs(16384, B, H, S, S, D, torch.bfloat16)
+    dout = attention_dout(16385, B, H, S, D, torch.bfloat16)
+    want = oracle.attention_bwd(q, k, v, dout, causal=True)
+    got, same = run_backward(q, k, v, dout, True, cuda_device)
+    check(got, same, want, "S=16384")

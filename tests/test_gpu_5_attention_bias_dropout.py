@@ -24,6 +24,15 @@ from helpers import DT, attention_dout, attention_inputs, golden_files, load_att
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(params=["ws64", "ws"])
+def impl(request):
+    """Forces one of the two warp-specialised forward kernels (each has bias / dropout variants of
+    its own; left alone the library picks by shape, which small tests would never vary)."""
+    L.attn_configure(impl=request.param)
+    yield request.param
+    L.attn_configure(impl="auto")
+
+
 def torch_same_precision(q, k, v, dout, causal, bias, keep, p):
     """Output and gradients with torch ops in the tensors' own 16-bit dtype
     (attention_ref with upcast=False, reorder_ops=True: tests/test_flash_attention_triton.py:107-117)."""
@@ -71,7 +80,7 @@ def check(got, same, want, what, rows=None):
 
 
 @pytest.mark.parametrize("path", golden_files("attnex"), ids=lambda p: p.split("attnex_")[-1][:-4])
-def test_bias_dropout_match_reference_vectors(cuda_device, path):
+def test_bias_dropout_match_reference_vectors(cuda_device, impl, path):
     g, q, k, v, dout, bias, keep = load_attention_ex_case(path)
     p = float(g["dropout_p"])
     rng = (int(g["rng_seed"]), int(g["rng_offset"]))
@@ -112,7 +121,7 @@ CASES = [
 
 @pytest.mark.parametrize("case", CASES, ids=lambda c: "B%dH%dSq%dSk%dD%d_%s_%s_%s_p%g" % (
     c[0], c[1], c[2], c[3], c[4], str(c[5])[6:], "causal" if c[6] else "full", c[7], c[9]))
-def test_bias_dropout_match_oracle(cuda_device, case):
+def test_bias_dropout_match_oracle(cuda_device, impl, case):
     B, H, Sq, Sk, D, dtype, causal, code, bias_dtype, p = case
     q, k, v = attention_inputs(900 + Sq + Sk, B, H, Sq, Sk, D, dtype)
     dout = attention_dout(31 + Sq, B, H, Sq, D, dtype)
@@ -136,6 +145,110 @@ def test_bias_dropout_match_oracle(cuda_device, case):
                                                  dout=dout)
     check(got, same, (out, dq, dk, dv), "oracle")
     assert torch.allclose(lse.cpu(), lse_o, atol=2e-3, rtol=1e-3)
+
+
+def _bias_of(code, B, H, Sq, Sk, seed, dtype=torch.float32):
+    shape = {"1h1k": (1, H, 1, Sk), "1hqk": (1, H, Sq, Sk), "b11k": (B, 1, 1, Sk), "b1qk": (B, 1, Sq, Sk)}[code]
+    gen = torch.Generator().manual_seed(seed)
+    bias = torch.randn(shape, generator=gen).to(dtype).float()
+    bias[..., 5::23] = float("-inf")
+    return bias
+
+
+def test_long_key_range_with_vector_bias_takes_the_128_key_kernel(cuda_device):
+    """Nothing forced: a bias without dropout over more than 48 key tiles is where the library
+    switches from the 64-key to the 128-key forward kernel.  Sk = 6272 is 49 tiles, not causal."""
+    L.attn_configure(impl="auto")
+    B, H, Sq, Sk, D = 1, 1, 384, 6272, 128
+    q, k, v = attention_inputs(77, B, H, Sq, Sk, D, torch.bfloat16)
+    dout = attention_dout(78, B, H, Sq, D, torch.bfloat16)
+    bias = _bias_of("1h1k", B, H, Sq, Sk, 79)
+    got, lse, same, _ = run_case(cuda_device, q, k, v, dout, False, bias, 0.0, None)
+    out, lse_o, dq, dk, dv = oracle.attention_ex(q, k, v, bias=bias, causal=False, dout=dout)
+    check(got, same, (out, dq, dk, dv), "49 key tiles, vector bias")
+    assert torch.allclose(lse.cpu(), lse_o, atol=2e-3, rtol=1e-3)
+    # and one tile fewer stays on the 64-key kernel: both sides of the switch agree with the oracle
+    q2, k2, v2 = q, k[:, :, :6144].contiguous(), v[:, :, :6144].contiguous()
+    bias2 = bias[..., :6144].contiguous()
+    got2, lse2, same2, _ = run_case(cuda_device, q2, k2, v2, dout, False, bias2, 0.0, None)
+    out2, lse_o2, dq2, dk2, dv2 = oracle.attention_ex(q2, k2, v2, bias=bias2, causal=False, dout=dout)
+    check(got2, same2, (out2, dq2, dk2, dv2), "48 key tiles, vector bias")
+    assert torch.allclose(lse2.cpu(), lse_o2, atol=2e-3, rtol=1e-3)
+
+
+# The reference's own grid (tests/test_flash_attention_triton.py:24-37): seqlen 3072, head_dim 128,
+# every bias shape, with and without dropout, with and without multi-query K/V.  Batch and heads
+# are kept at 2 x 2 so that the CPU oracle stays within seconds per case.
+REF_GRID = [(code, p, mq) for code in (None, "1h1k", "b11k", "1hqk", "b1qk") for p, mq in ((0.0, False), (0.17, True))]
+REF_GRID += [(None, 0.17, False), ("1h1k", 0.17, False), ("1hqk", 0.0, True)]
+
+
+@pytest.mark.parametrize("code,p,mq", REF_GRID, ids=lambda x: str(x))
+@pytest.mark.parametrize("causal", [True, False], ids=["causal", "full"])
+def test_reference_grid_seqlen_3072(cuda_device, code, p, mq, causal):
+    if causal != (code in (None, "1h1k", "b1qk")):
+        pytest.skip("each bias shape runs with one mask setting, alternating")
+    L.attn_configure(impl="auto")
+    B, H, S, D = 2, 2, 3072, 128
+    dtype = torch.bfloat16
+    q, k, v = attention_inputs(3072 + len(str(code)), B, H, S, S, D, dtype)
+    if mq:  # one K/V head shared by all query heads, expanded with stride 0 as the reference's tests do
+        k, v = k[:, :1].expand(B, H, S, D), v[:, :1].expand(B, H, S, D)
+    dout = attention_dout(3073, B, H, S, D, dtype)
+    bias = None if code is None else _bias_of(code, B, H, S, S, 3074)
+    rng = (0, 16773120 + 4096 - (B * H * S * S) // 2 // 4 * 4) if p > 0 else None
+    dev = cuda_device
+    qd, dd = q.to(dev), dout.to(dev)
+    kd = k[:, :1].contiguous().to(dev).expand(B, H, S, D) if mq else k.to(dev)
+    vd = v[:, :1].contiguous().to(dev).expand(B, H, S, D) if mq else v.to(dev)
+    bd = None if bias is None else bias.to(dev)
+    o, lse = flash_attention_forward(qd, kd, vd, causal=causal, return_lse=True, bias=bd, dropout_p=p, rng=rng)
+    dq, dk, dv = flash_attention_backward(dd, qd, kd, vd, o, lse, causal=causal, bias=bd, dropout_p=p, rng=rng)
+    torch.cuda.synchronize()
+    assert L.device_status(dev.index) == 0, "a kernel wait timed out"
+    keep = dropout_mask(p, B, H, S, S, dev, rng=rng) if p > 0 else None
+    keep_cpu = None
+    if p > 0:
+        keep_cpu = oracle.dropout_mask(p, B, H, S, S, *rng)
+        assert torch.equal(keep.cpu(), keep_cpu)
+        assert 0.05 < keep_cpu.float().mean().item() < 0.95
+    same = torch_same_precision(qd, kd.contiguous(), vd.contiguous(), dd, causal, bd, keep, p)
+    want = oracle.attention_ex(q, k.contiguous(), v.contiguous(), bias=bias, keep_mask=keep_cpu, dropout_p=p,
+                               causal=causal, dout=dout)
+    check((o, dq, dk, dv), same, (want[0], want[2], want[3], want[4]), f"S=3072 {code} p={p} mq={mq}")
+    assert torch.allclose(lse.cpu(), want[1], atol=2e-3, rtol=1e-3)
+
+
+def test_bshd_entry_returns_q_layout_with_and_without_grad(cuda_device):
+    """The reference allocates O with q's layout (flash_attention_triton.py:773): for ordinary
+    contiguous (B, S, H, D) inputs `out.view(B, S, H * D)` must work in training and in eval."""
+    B, S, H, D = 2, 200, 3, 64
+    gen = torch.Generator().manual_seed(12)
+    q, k, v = (torch.randn(B, S, H, D, generator=gen).half().to(cuda_device) for _ in range(3))
+    assert q.is_contiguous()
+    with torch.no_grad():
+        o_eval = flash_attn_triton(q, k, v, None, True)
+    qg = q.clone().requires_grad_(True)
+    o_train = flash_attn_triton(qg, k, v, None, True)
+    for o in (o_eval, o_train):
+        assert o.shape == (B, S, H, D) and o.is_contiguous() and o.stride() == q.stride()
+        o.view(B, S, H * D)
+    assert torch.equal(o_eval, o_train.detach())
+    o_train.sum().backward()
+    assert qg.grad is not None and qg.grad.shape == q.shape
+
+
+def test_generator_advances_on_every_bshd_forward(cuda_device):
+    """increment_philox_state runs on every forward of the reference, with or without dropout
+    (flash_attention_triton.py:780); later draws from the generator then match a reference run."""
+    B, S, H, D = 1, 130, 2, 64
+    q, k, v = (torch.randn(B, S, H, D, device=cuda_device, dtype=torch.float16) for _ in range(3))
+    with torch.cuda.device(cuda_device):
+        torch.cuda.manual_seed(5)
+        before = next_dropout_rng(cuda_device, 0)
+        flash_attn_triton(q, k, v)  # dropout_p = 0
+        after = next_dropout_rng(cuda_device, 0)
+    assert after[0] == before[0] and after[1] == before[1] + (B * H * S * S + 3) // 4 * 4
 
 
 @pytest.mark.parametrize("code", ["1h1k", "b1qk"])

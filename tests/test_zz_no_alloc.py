@@ -14,6 +14,7 @@ import pytest
 import torch
 
 import fast_ops_b200._lib as L
+import oracle
 
 pytestmark = pytest.mark.gpu
 
@@ -50,6 +51,7 @@ def test_noalloc_matches_allocating_entry_point_twice_in_a_row(cuda_device):
     for i, (shapes, pd, md, hyper) in enumerate(calls):
         p1, g1, m1 = _make(shapes, pd, md, 100 + i, cuda_device)
         p2, m2 = [t.clone() for t in p1], [t.clone() for t in m1]
+        p3, g3, m3 = ([t.cpu().reshape(-1).clone() for t in ts] for ts in (p1, g1, m1))  # the CPU oracle's copy
         for _ in range(2):  # two steps each, so the momentum written by step 1 feeds step 2
             _run(lib.fo_lion_multi_tensor_step, p1, g1, m1, pd, md, hyper, cuda_device)
             _run(lib.fo_lion_multi_tensor_step_noalloc, p2, g1, m2, pd, md, hyper, cuda_device)
@@ -58,6 +60,14 @@ def test_noalloc_matches_allocating_entry_point_twice_in_a_row(cuda_device):
             assert torch.equal(a, b), f"call {i}: parameters differ"
         for a, b in zip(m1, m2):
             assert torch.equal(a, b), f"call {i}: momentum differs"
+        # and against the reference arithmetic itself, not only against the other entry point
+        for _ in range(2):
+            for cp, cg, cm in zip(p3, g3, m3):
+                if cp.numel():
+                    oracle.lion_step(cp, cg, cm, hyper[0], (hyper[1], hyper[2]), hyper[3])
+        for a, cp, b, cm in zip(p2, p3, m2, m3):
+            assert torch.equal(a.cpu().reshape(-1), cp), f"call {i}: parameters differ from the oracle"
+            assert torch.equal(b.cpu().reshape(-1), cm), f"call {i}: momentum differs from the oracle"
 
 
 def test_noalloc_rejects_lists_beyond_its_maximum(cuda_device):
@@ -71,3 +81,31 @@ def test_noalloc_rejects_lists_beyond_its_maximum(cuda_device):
     assert rc == -1 and b"at most 1024 tensors" in lib.fo_last_error()
     torch.cuda.synchronize()
     assert torch.equal(t.cpu(), torch.zeros(8, dtype=torch.bfloat16)), "a rejected call must not launch"
+
+
+def test_noalloc_refuses_a_capturing_stream(cuda_device):
+    """Captured into a CUDA graph, the table upload would become a node that re-reads the
+    library's single host-side table image at every replay, when it describes whichever list was
+    passed last; the entry point refuses instead of replaying the wrong list."""
+    lib = L.load()
+    shapes = [(4096,), (100,)]
+    p, g, m = _make(shapes, torch.bfloat16, torch.bfloat16, 7, cuda_device)
+    hyper = (1e-4, 0.9, 0.99, 0.1)
+    _run(lib.fo_lion_multi_tensor_step_noalloc, p, g, m, torch.bfloat16, torch.bfloat16, hyper, cuda_device)  # set-up call
+    torch.cuda.synchronize()
+    before = [t.clone() for t in p]
+    ap, ag, am, an, n = _arrays(p, g, m)
+    stream = torch.cuda.Stream(cuda_device)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        graph.capture_begin()
+        try:
+            rc = lib.fo_lion_multi_tensor_step_noalloc(ap, ag, am, an, n, L.FO_BF16, L.FO_BF16, L.FO_BF16, *hyper,
+                                                       cuda_device.index, stream.cuda_stream)
+            message = lib.fo_last_error()
+        finally:
+            graph.capture_end()
+    assert rc == -3 and b"capturing" in message  # FO_ERR_UNSUPPORTED
+    torch.cuda.synchronize()
+    for a, b in zip(p, before):
+        assert torch.equal(a, b), "a refused call must not change anything"
