@@ -212,12 +212,42 @@ def attn_inputs(B, H, S, D, device, seed):
                  for _ in range(3))
 
 
-def bench_attention(d: Dist, name: str, steps: int, warmup: int, peaks, with_e2e=True, with_clocks=True):
+def attention_config(name: str, world: int, split: str):
+    """The `config` object of an attention line (the GPU arm and the CPU reference arm print the same)."""
+    B, H, S, D, causal = ATTN[name]
+    strong = split == "strong" and world > 1
+    heads = B * H // world if strong else B * H
+    where = (f"the {B * H} (batch, head) pairs split {heads} per GPU over {world} GPUs" if strong else "per GPU")
+    input_bytes = 3 * heads * S * D * 2
+    flush = input_bytes <= 2 * 126e6
+    return {"workload": f"{name}: attention fwd B={B} H={H} S={S} D={D} bf16 causal={causal}, {where}",
+            "global_batch": B if strong else B * world,
+            "l2": ("L2 flushed (512 MB written) before every timed step" if flush
+                   else "inputs (%.0f MB) larger than L2, no flush" % (input_bytes / 1e6))}
+
+
+def bench_attention(d: Dist, name: str, steps: int, warmup: int, peaks, with_e2e=True, with_clocks=True,
+                    split="weak"):
+    """Forward of one attention workload.  split="weak": every rank runs the whole (B, H) shape on
+    its own inputs.  split="strong": the B*H (batch, head) pairs of the ONE configured shape are
+    divided over the ranks, rank r taking pairs [r*B*H/N, (r+1)*B*H/N) (pairs are independent:
+    fast_ops/flash_attention/flash_attention_fwd.cu:57-59 indexes its grid by them), no collective;
+    `value` is then the shape's FLOPs over the slowest rank's time."""
     import fast_ops_b200._lib as L
     from fast_ops_b200.flash_attention import flash_attention_forward
 
     B, H, S, D, causal = ATTN[name]
-    q, k, v = attn_inputs(B, H, S, D, d.device, seed=1000 + d.rank)
+    flops_shape = attn_flops(B, H, S, D, causal)
+    if split == "strong" and d.world > 1:
+        if (B * H) % d.world:
+            raise SystemExit(f"{B * H} (batch, head) pairs do not divide over {d.world} ranks")
+        Bl, Hl = 1, B * H // d.world  # this rank's pairs, as heads of one batch entry
+        flops_rank, flops_job = flops_shape / d.world, flops_shape
+    else:
+        split = "weak"
+        Bl, Hl = B, H
+        flops_rank, flops_job = flops_shape, flops_shape * d.world
+    q, k, v = attn_inputs(Bl, Hl, S, D, d.device, seed=1000 + d.rank)
     lib = L.load()
     fn = lambda: flash_attention_forward(q, k, v, causal=causal)  # noqa: E731
     launches0 = lib.fo_launch_count()
@@ -228,18 +258,15 @@ def bench_attention(d: Dist, name: str, steps: int, warmup: int, peaks, with_e2e
     launches = (lib.fo_launch_count() - launches0 - warmup)
     if L.device_status(d.local_rank) != 0:
         raise RuntimeError("an attention kernel reported a timed-out wait")
-    flops = attn_flops(B, H, S, D, causal)
-    tflops_rank = flops / (ms * 1e-3) / 1e12
+    tflops_rank = flops_rank / (ms * 1e-3) / 1e12
     out = {
-        "value": tflops_rank * d.world, "ms_per_step": ms, "gpu_launches": launches, "clocks": clocks,
+        "value": flops_job / (ms * 1e-3) / 1e12, "ms_per_step": ms, "gpu_launches": launches, "clocks": clocks,
+        "scaling": split,
         "roofline": {"bound": "tensor", "achieved": tflops_rank, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                      "frac": tflops_rank / peaks["bf16_tflops"], "traffic": measured_traffic(name),
                      "peak_source": peaks["source"] + " cuBLAS bf16 burst",
                      "frac_of_sustained": tflops_rank / peaks["bf16_tflops_sustained"]},
-        "config": {"workload": f"{name}: attention fwd B={B} H={H} S={S} D={D} bf16 causal={causal}, per GPU",
-                   "global_batch": B * d.world,
-                   "l2": ("L2 flushed (512 MB written) before every timed step" if flush
-                          else "inputs (%.0f MB) larger than L2, no flush" % (input_bytes / 1e6))},
+        "config": attention_config(name, d.world, split),
     }
     if with_e2e:
         # public call on HOST buffers: H2D of Q, K, V, forward, D2H of O, every step (the host
@@ -257,7 +284,7 @@ def bench_attention(d: Dist, name: str, steps: int, warmup: int, peaks, with_e2e
 
         e2e_steps = max(2, min(steps, 5))
         ms_e2e, _ = timed_steps(d, e2e_step, e2e_steps, 1)
-        out["e2e"] = {"value": flops / (ms_e2e * 1e-3) / 1e12 * d.world, "unit": "TFLOP/s",
+        out["e2e"] = {"value": flops_job / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
                       "h2d_bytes_per_step": 3 * hq.numel() * 2, "d2h_bytes_per_step": ho.numel() * 2,
                       "ms_per_step": ms_e2e, "steps": e2e_steps}
     return out
@@ -316,17 +343,81 @@ def bench_attention_variants(d: Dist, name: str, steps: int, warmup: int, peaks)
 
 def bench_attention_sweep(d: Dist, steps: int, warmup: int, peaks):
     """The metric's sweep: bf16 causal forward, H=32, D=128, batch x sequence = 32768 tokens, so that
-    every point reads the same 805 MB (larger than L2): TFLOP/s per GPU by sequence length."""
+    every point reads the same 805 MB (larger than L2): TFLOP/s per GPU by sequence length.  Every
+    point carries the median SM clock sampled while it ran, so that points taken at different
+    clocks (the power cap moves them) can be compared as time x MHz."""
     from fast_ops_b200.flash_attention import flash_attention_forward
 
     out = {"workload": "attention fwd bf16 causal, H=32 D=128, B*S=32768 tokens per GPU", "unit": "TFLOP/s per GPU"}
     for S in (1024, 2048, 4096, 8192, 16384):
         B = 32768 // S
         q, k, v = attn_inputs(B, 32, S, 128, d.device, seed=7000 + S + d.rank)
-        ms, _ = timed_steps(d, lambda: flash_attention_forward(q, k, v, causal=True), steps, warmup)
+        sampler = ClockSampler(d.local_rank, period_s=0.002)
+        ms, clocks = timed_steps(d, lambda: flash_attention_forward(q, k, v, causal=True), steps, warmup, sampler)
         tf = attn_flops(B, 32, S, 128, True) / (ms * 1e-3) / 1e12
-        out[f"S{S}"] = {"value": tf, "ms_per_step": ms, "frac": tf / peaks["bf16_tflops"]}
+        out[f"S{S}"] = {"value": tf, "ms_per_step": ms, "frac": tf / peaks["bf16_tflops"],
+                        "sm_mhz": clocks["sm_mhz"], "reasons": clocks["reasons"]}
         del q, k, v
+    return out
+
+
+# A100 figures the reference publishes (wall-clock microseconds): fast_ops/lion/README.md:32-35
+# ("ours" column) and fast_ops/flash_attention/README.md:80-97 (Triton forward, bf16, (1,12,S,128)).
+PUBLISHED_A100_US = {
+    "lion_8192_f16": 25.1, "lion_8192_bf16": 25.0, "lion_67108864_f16": 651.9, "lion_67108864_bf16": 710.1,
+    "attn_S2048_full": 258.2, "attn_S2048_causal": 188.7, "attn_S4096_full": 926.5, "attn_S4096_causal": 548.9,
+    "attn_S8192_full": 3415.7, "attn_S8192_causal": 1788.7,
+}
+
+
+def bench_reference_points(d: Dist):
+    """The reference's own benchmark points, timed the way its scripts time them: wall clock of
+    the public call with torch.utils.benchmark (which synchronises the device around the timed
+    statement), median of a blocked autorange.  Lion: `lion.step()` on one tensor of 8192 and
+    8192^2 elements, fp16 and bf16 (benchmarks/benchmark_lion.py:11-37).  Attention: forward of
+    (batch 1, 12 heads, S, head_dim 128) bf16 in (B, S, H, D) layout, S in 2048/4096/8192, causal and
+    not (benchmarks/benchmark_flash_attention.py:90; fast_ops/flash_attention/README.md:67-97)."""
+    from torch.utils.benchmark import Timer
+
+    from fast_ops.flash_attention.flash_attention_triton import flash_attn_triton
+    from fast_ops.lion.lion_optimizer import Lion
+
+    out = {"method": "torch.utils.benchmark.Timer.blocked_autorange median, wall clock of the public call",
+           "unit": "us", "published": "A100 wall-clock figures from the reference's READMEs"}
+    with torch.cuda.device(d.device):
+        for size in (8192, 8192 ** 2):
+            for dtype, tag in ((torch.float16, "f16"), (torch.bfloat16, "bf16")):
+                params = [torch.randn(size, dtype=dtype, device=d.device)]
+                params[0].grad = torch.randn_like(params[0])
+                lion = Lion(params, lr=1e-4, betas=(0.9, 0.99), weight_decay=0.1)
+                lion.step()
+                m = Timer(stmt="lion.step()", globals={"lion": lion}).blocked_autorange(min_run_time=0.3)
+                us = m.median * 1e6
+                key = f"lion_{size}_{tag}"
+                out[key] = {"us": us, "a100_us": PUBLISHED_A100_US[key], "speedup_vs_a100": PUBLISHED_A100_US[key] / us,
+                            "gbs": size * 10 / (us * 1e-6) / 1e9}
+                del params, lion
+        for S in (2048, 4096, 8192):
+            q, k, v = (torch.randn(1, S, 12, 128, dtype=torch.bfloat16, device=d.device) for _ in range(3))
+            for causal, tag in ((False, "full"), (True, "causal")):
+                with torch.no_grad():
+                    flash_attn_triton(q, k, v, None, causal)
+                    m = Timer(stmt="f(q, k, v, None, causal)",
+                              globals={"f": flash_attn_triton, "q": q, "k": k, "v": v, "causal": causal}
+                              ).blocked_autorange(min_run_time=0.3)
+                us = m.median * 1e6
+                key = f"attn_S{S}_{tag}"
+                flops = attn_flops(1, 12, S, 128, causal)
+                out[key] = {"us": us, "a100_us": PUBLISHED_A100_US[key], "speedup_vs_a100": PUBLISHED_A100_US[key] / us,
+                            "tflops": flops / (us * 1e-6) / 1e12}
+            del q, k, v
+        # what one call costs on the host when the kernel is negligible (one 128-row tile)
+        q = torch.randn(1, 1, 128, 64, dtype=torch.bfloat16, device=d.device)
+        from fast_ops_b200.flash_attention import flash_attention_forward
+
+        m = Timer(stmt="f(q, q, q, causal=True)", globals={"f": flash_attention_forward, "q": q}
+                  ).blocked_autorange(min_run_time=0.3)
+        out["attention_call_floor_us"] = m.median * 1e6
     return out
 
 
@@ -417,10 +508,63 @@ def bench_lion_c4(d: Dist, steps: int, warmup: int, peaks, with_e2e=True):
     return res
 
 
+def buffer_hash(t):
+    """Position-weighted 64-bit checksum of a 16-bit tensor's bit patterns (wraps modulo 2^64),
+    computed on its device in bounded pieces."""
+    bits = t.view(torch.int16)
+    piece = 1 << 26
+    w = (torch.arange(piece, device=t.device, dtype=torch.int64) % 65521) + 1
+    acc = torch.zeros((), device=t.device, dtype=torch.int64)
+    for off in range(0, bits.numel(), piece):
+        m = min(piece, bits.numel() - off)
+        acc = acc * 31 + (bits[off:off + m].to(torch.int64) * w[:m]).sum()
+    return acc
+
+
+def zero1_parity_check(d: Dist, flat_p, flat_g, m_shard, begin, end, step_fn, hyper):
+    """Runs ONE more ZeRO-1 step (outside any timed region) and checks it: a 2^20-element window in
+    the middle of this rank's shard must equal the CPU oracle's step on the window's previous
+    contents, bit for bit, and afterwards every rank must hold the same flat parameter buffer
+    (checksums agree).  Returns "ok", or a description of the failure: it never raises, so that a
+    rank does not leave while peers still have its memory mapped; main() turns a failure into a
+    non-zero exit after the process group has been shut down."""
+    import oracle
+
+    lr, betas, wd = hyper
+    w = min(1 << 20, end - begin)
+    a = begin + ((end - begin - w) // 2) // 8 * 8
+    p0, g0 = flat_p[a:a + w].cpu(), flat_g[a:a + w].cpu()
+    m0 = m_shard[a - begin:a - begin + w].cpu()
+    step_fn()
+    torch.cuda.synchronize()
+    oracle.lion_step(p0, g0, m0, lr, betas, wd)
+    bad = 0
+    if not torch.equal(flat_p[a:a + w].cpu(), p0):
+        bad |= 1
+    if not torch.equal(m_shard[a - begin:a - begin + w].cpu(), m0):
+        bad |= 2
+    if d.on:
+        h = buffer_hash(flat_p)
+        lo, hi = h.clone(), h.clone()
+        d.dist.all_reduce(lo, op=d.dist.ReduceOp.MIN)
+        d.dist.all_reduce(hi, op=d.dist.ReduceOp.MAX)
+        if int(lo.item()) != int(hi.item()):
+            bad |= 4
+        flags = torch.tensor([bad], device=d.device)
+        d.dist.all_reduce(flags, op=d.dist.ReduceOp.BOR)
+        bad = int(flags.item())
+    if bad == 0:
+        return "ok"
+    what = [name for bit, name in ((1, "parameters differ from the oracle"), (2, "momentum differs from the oracle"),
+                                   (4, "the ranks' flat buffers differ")) if bad & bit]
+    return "FAILED: " + "; ".join(what)
+
+
 def bench_lion_c5(d: Dist, steps: int, warmup: int, peaks):
     """Llama-7B list, bf16 p/g/m, 10 algorithmic bytes per parameter, ZeRO-1: each rank updates
     1/N of one flat buffer, then ONE NCCL all-gather of the updated bf16 weights.  Total work is
-    fixed as N grows."""
+    fixed as N grows.  After the timed loops one more step is checked against the oracle and
+    across the ranks (`parity_check`)."""
     import fast_ops_b200._lib as L
     from fast_ops_b200.lion import FlatLayout
     from fast_ops_b200.lion.lion_optimizer import _flat_step
@@ -429,7 +573,7 @@ def bench_lion_c5(d: Dist, steps: int, warmup: int, peaks):
     layout = FlatLayout.build([numel(s) for s in shapes], d.world)
     n = sum(numel(s) for s in shapes)
     total = layout.total
-    gen = torch.Generator(device=d.device).manual_seed(11)
+    gen = torch.Generator(device=d.device).manual_seed(11)  # the same on every rank: replicas start equal
     flat_p = torch.empty(total, device=d.device, dtype=torch.bfloat16)
     flat_g = torch.empty(total, device=d.device, dtype=torch.bfloat16)
     piece = 1 << 28
@@ -440,9 +584,10 @@ def bench_lion_c5(d: Dist, steps: int, warmup: int, peaks):
     begin, end = layout.shard_range(d.rank)
     m_shard = torch.zeros(end - begin, device=d.device, dtype=torch.bfloat16)
     lib = L.load()
+    hyper = (3e-5, (0.9, 0.99), 0.1)
 
     def step_kernel():
-        _flat_step(flat_p, flat_g, m_shard, begin, end, 3e-5, (0.9, 0.99), 0.1)
+        _flat_step(flat_p, flat_g, m_shard, begin, end, *hyper)
 
     def gather():
         if d.on:
@@ -457,12 +602,14 @@ def bench_lion_c5(d: Dist, steps: int, warmup: int, peaks):
     launches = lib.fo_launch_count() - l0 - warmup
     ms_kernel, _ = timed_steps(d, step_kernel, steps, 1)
     ms_gather = timed_steps(d, gather, steps, 1)[0] if d.on else 0.0
+    parity = zero1_parity_check(d, flat_p, flat_g, m_shard, begin, end, full_step, hyper)
     shard_bytes = (end - begin) * 10
     res = {"workload": f"lion_c5: Llama-7B list, {len(shapes)} tensors, {n} params, bf16 p/g/m, ZeRO-1 over "
                        f"{d.world} GPU(s) + all-gather of bf16 weights",
            "scaling": "strong",
            "value": n * 10 / (ms_full * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms_full, "gpu_launches": launches,
            "kernel_ms": ms_kernel, "kernel_gbs_per_gpu": shard_bytes / (ms_kernel * 1e-3) / 1e9,
+           "parity_check": parity,
            "roofline": {"bound": "hbm", "achieved": shard_bytes / (ms_kernel * 1e-3) / 1e9, "peak": peaks["hbm_gbs"],
                         "unit": "GB/s", "frac": shard_bytes / (ms_kernel * 1e-3) / 1e9 / peaks["hbm_gbs"],
                         "traffic": None, "peak_source": peaks["source"] + " copy"}}
@@ -485,13 +632,15 @@ def bench_lion_c5(d: Dist, steps: int, warmup: int, peaks):
 
             def fused_step():
                 hdl.barrier(channel=0)
-                _flat_step_push(sym_p, flat_g, m_shard, begin, end, peers, 3e-5, (0.9, 0.99), 0.1)
+                _flat_step_push(sym_p, flat_g, m_shard, begin, end, peers, *hyper)
                 hdl.barrier(channel=1)
 
             ms_fused, _ = timed_steps(d, fused_step, steps, warmup)
             res["fused_gather"] = {"ms_per_step": ms_fused, "value": n * 10 / (ms_fused * 1e-3) / 1e9, "unit": "GB/s",
                                    "nvlink_egress_gbs_per_gpu": recv / (ms_fused * 1e-3) / 1e9,
-                                   "speedup_vs_step_plus_all_gather": ms_full / ms_fused}
+                                   "speedup_vs_step_plus_all_gather": ms_full / ms_fused,
+                                   "parity_check": zero1_parity_check(d, sym_p, flat_g, m_shard, begin, end,
+                                                                      fused_step, hyper)}
         except Exception as exc:  # symmetric memory unavailable: report, keep the NCCL numbers
             res["fused_gather"] = {"unavailable": repr(exc)[:200]}
     del flat_p, flat_g, m_shard
@@ -530,15 +679,15 @@ def run_reference_arm(args):
     if name.startswith("attn"):
         stride = 4 if name == "attn_c3" else 1
         cpu, _ = cpu_attention_sample(name, stride, max(1, args.steps))
-        B, H, S, D, causal = ATTN[name]
-        work = f"{name}: attention fwd B={B} H={H} S={S} D={D} bf16 causal={causal}, per GPU"
+        split = "strong" if (name == "attn_c3" and args.gpus > 1) else "weak"
+        config = attention_config(name, args.gpus, split)
         metric, unit = "attention_fwd_tflops", "TFLOP/s"
     else:
         cpu = cpu_lion_sample(max(1, args.steps))
-        work, metric, unit = name, "lion_step_hbm_gbs", "GB/s"
+        config, metric, unit, split = {"workload": name}, "lion_step_hbm_gbs", "GB/s", "weak"
     line = {"impl": "reference", "metric": metric, "value": cpu["value"], "unit": unit, "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": {"workload": work},
+            "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "scaling": split,
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
             "cpu_baseline": cpu,
             "e2e": {"value": cpu["value"], "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
@@ -574,8 +723,10 @@ def main():
                      "config": {"workload": r.pop("workload"), "l2": "inputs larger than L2"}})
         line.update(r)
     elif args.workload.startswith("attn"):
-        r = bench_attention(d, args.workload, args.steps, args.warmup, peaks, with_e2e=not args.no_e2e)
-        line.update({"metric": "attention_fwd_tflops", "unit": "TFLOP/s", "scaling": "weak", "dtype": "bf16"})
+        # the long-context shape is ONE job split over the GPUs (strong scaling); the others run per GPU
+        split = "strong" if args.workload == "attn_c3" else "weak"
+        r = bench_attention(d, args.workload, args.steps, args.warmup, peaks, with_e2e=not args.no_e2e, split=split)
+        line.update({"metric": "attention_fwd_tflops", "unit": "TFLOP/s", "dtype": "bf16"})
         line.update(r)
     elif args.workload == "lion_c4":
         r = bench_lion_c4(d, args.steps, args.warmup, peaks, with_e2e=not args.no_e2e)
@@ -594,6 +745,11 @@ def main():
             a = bench_attention(d, "attn_c2", max(args.steps, 50), args.warmup, peaks, with_e2e=False, with_clocks=False)
             also["attn_c2"] = {k: a[k] for k in ("value", "ms_per_step", "roofline", "config")}
             also["attn_c2"]["unit"] = "TFLOP/s"
+        if args.workload == "attn_c3" and d.world > 1:
+            a = bench_attention(d, "attn_c3", max(3, args.steps // 2), args.warmup, peaks, with_e2e=False,
+                                with_clocks=False, split="weak")
+            also["attn_c3_weak"] = {k: a[k] for k in ("value", "ms_per_step", "scaling", "roofline", "config")}
+            also["attn_c3_weak"]["unit"] = "TFLOP/s"
         if not args.workload.startswith("attn_bwd"):
             also["attn_bwd_c3"] = bench_attention_bwd(d, "attn_c3", max(3, args.steps // 4), 2, peaks)
             also["attn_bias_dropout_c3"] = bench_attention_variants(d, "attn_c3", max(3, args.steps // 4), 2, peaks)
@@ -602,6 +758,8 @@ def main():
             also["lion_c4"] = bench_lion_c4(d, args.steps, args.warmup, peaks)
         if args.workload != "lion_c5":
             also["lion_c5"] = bench_lion_c5(d, max(3, args.steps // 4), 2, peaks)
+        if d.world == 1:
+            also["reference_points"] = bench_reference_points(d)
         line["also"] = also
 
     if d.rank == 0 and d.world == 1 and not args.no_cpu:
@@ -616,6 +774,10 @@ def main():
     d.close()
     if d.rank == 0:
         print(json.dumps(line), flush=True)
+    # a failed ZeRO-1 self-check fails the run, after every rank has left the group in order
+    text = json.dumps(line)
+    if '"parity_check": "FAILED' in text:
+        raise SystemExit("ZeRO-1 parity check failed: see parity_check in the line above")
 
 
 if __name__ == "__main__":

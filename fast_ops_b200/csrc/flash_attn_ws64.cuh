@@ -207,7 +207,6 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     if (ping_pong && s == 1) named_barrier_arrive(kTurn0, kTurnCount);
 
     uint32_t sr[2][32];  // scores of the current step (scaled and biased already when there is a bias)
-    float mx = -INFINITY;  // their row maximum
 
     // Stages the row-independent bias of the key tile that step `tn` (even) starts.
     auto stage_vec_bias = [&](int tn) {
@@ -223,15 +222,14 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       const uint32_t tSn = tS_tile + (tn & 1) * kStepN;
       tmem_ld32(tSn + c * 32, sr[c]);
     };
-    // Waits for those loads, applies bias and masks in place and reduces the row maximum.
-    auto finish_loads = [&](int tn) {
+    // Waits for those loads and applies bias and masks in place.
+    auto prep_loads = [&](int tn) {
       const int k0n = tn * kStepN;
       const bool need_mask = (k0n + kStepN > prm.Sk) || (prm.causal && k0n + kStepN - 1 > q0);
-      float mxa = -INFINITY, mxb = -INFINITY, mxc = -INFINITY, mxd = -INFINITY;
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         tmem_ld_wait(sr[c]);
-        if ((warp & 3) == 0 && tn > 0) trace_event(prm, s, tn - 1, c == 0 ? 1 : 4);  // loads in / half reduced
+        if ((warp & 3) == 0 && tn > 0) trace_event(prm, s, tn - 1, c == 0 ? 1 : 4);  // loads in
         if constexpr (kExt != 0) {
           if (vec_bias) {
             const float4* bv = reinterpret_cast<const float4*>(sb + ((tn >> 1) & 1) * 128 + (tn & 1) * kStepN + c * 32);
@@ -258,7 +256,14 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             if (col >= prm.Sk || (prm.causal && col > row)) sr[c][i] = 0xff800000u;  // -inf
           }
         }
-        // four independent accumulators (and 3-input max) keep the dependency chain short
+      }
+    };
+    // Row maximum of the scores in sr: four independent accumulators (and 3-input max) keep the
+    // dependency chain short.
+    auto row_max = [&]() {
+      float mxa = -INFINITY, mxb = -INFINITY, mxc = -INFINITY, mxd = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
 #pragma unroll
         for (int i = 0; i < 32; i += 8) {
           mxa = max3(mxa, __uint_as_float(sr[c][i + 0]), __uint_as_float(sr[c][i + 1]));
@@ -267,10 +272,10 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           mxd = max3(mxd, __uint_as_float(sr[c][i + 6]), __uint_as_float(sr[c][i + 7]));
         }
       }
-      mx = fmaxf(fmaxf(mxa, mxb), fmaxf(mxc, mxd));
+      return fmaxf(fmaxf(mxa, mxb), fmaxf(mxc, mxd));
     };
 
-    // prologue: scores and maximum of step 0
+    // prologue: scores of step 0; their row maximum is the first reference maximum
     if constexpr (kExt != 0) {
       if (vec_bias) stage_vec_bias(0);
     }
@@ -278,67 +283,89 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     tcgen05_fence_after_sync();
     issue_load(0, 0);
     issue_load(0, 1);
-    finish_loads(0);
+    prep_loads(0);
+    m_run = row_max() * exp_scale;
 
-    // Each iteration exponentiates step t and, behind the exponentials, fetches and reduces step
-    // t + 1 (whose S the tensor core finished meanwhile), so that the latencies of the loads, of
-    // the P store and of the barriers overlap instead of adding up.
+    // The exponentials of a step do not wait for the step's own row maximum: they are taken
+    // against the reference maximum the row already has (lazy rescaling moves it only when the
+    // true maximum exceeds it by kRescaleThreshold), and the maximum is reduced alongside them,
+    // its instructions filling issue slots that the ex2 unit's rate leaves empty.  Only if a row
+    // of the warp turns out to need a new reference (rare after the first steps) are the step's
+    // exponentials taken again.  Each iteration then fetches step t + 1 (whose S the tensor core
+    // finished meanwhile) behind the P stores, so that the latencies of the loads, of the P store
+    // and of the barriers overlap instead of adding up.
     for (int t = 0; t < T_s; ++t) {
       const int u = t & 1;
       const int k0 = t * kStepN;
       const uint32_t tS = tS_tile + u * kStepN;
-      const float m_cand = fmaxf(m_run, mx * exp_scale);
-      const float m_new = (m_cand - m_run > kRescaleThreshold) ? m_cand : m_run;
-      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      // The rescale factor is 1 for every row of the warp in nearly all steps (lazy rescaling):
-      // a warp-uniform branch keeps its ex2 out of the way then.  It would otherwise queue behind
-      // the other tile's exponentials on the same unit and, issue being in order, hold up
-      // everything below.
-      float alpha = 1.f;
-      if (__any_sync(0xffffffffu, m_new != m_run)) alpha = (m_new == m_run) ? 1.f : fast_exp2(m_run - m_use);
-      float neg_m = -m_use;
+      float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;
       if (ping_pong) named_barrier_sync_dep(s ? kTurn1 : kTurn0, kTurnCount, neg_m);  // exponentials start after this
-      // hand the rescale factor to the correction warps (off this thread's critical path)
-      alpha_slot[u * 128] = alpha;
-      mbar_arrive(bar_corr + 2 * s + u);
       if ((warp & 3) == 0) trace_event(prm, s, t, 0);  // turn taken
       const float2 sc2 = make_float2(exp_scale, exp_scale);
-      const float2 nm2 = make_float2(neg_m, neg_m);
-      float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
+      float2 acc0, acc1;
       uint32_t pr[2][16];
       const bool more = t + 1 < T_s;
       bool s_next_ready = false;
+      float mxa = -INFINITY, mxb = -INFINITY;
+      // P = exp2(S * scale - reference) for the whole step; `first` is the pass that also passes
+      // the turn on, polls the next S and reduces the row maximum
+      auto exp_pass = [&](float neg_ref, const bool first) {
+        const float2 nm2 = make_float2(neg_ref, neg_ref);
+        acc0 = make_float2(0.f, 0.f);
+        acc1 = make_float2(0.f, 0.f);
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        // one non-blocking look at S of step t + 1 (as a rule complete by now); the answer is
-        // needed only after the exponentials, so its latency is hidden
-        if (c == 1 && more) s_next_ready = mbar_test_wait(bar_s_full + 2 * s + (u ^ 1), ((t + 1) >> 1) & 1);
-        // The turn is passed on after the first half (the partial row sums depend on all of its
-        // exponentials): the other tile's first half then shares the ex2 units with this tile's
-        // second half, two warps per scheduler, which hides the latencies a lone warp exposes.
-        float2 nm2c = nm2;
-        if (c == 1 && ping_pong) {
-          named_barrier_arrive_mid(s ? kTurn0 : kTurn1, kTurnCount, neg_m, acc0.x + acc0.y, acc1.x + acc1.y);
-          nm2c = make_float2(neg_m, neg_m);  // the second half's arithmetic hangs on the arrive
-        }
-#pragma unroll
-        for (int q = 0; q < 16; ++q) {  // column pair q of the chunk
-          float2 x = __ffma2_rn(make_float2(__uint_as_float(sr[c][2 * q]), __uint_as_float(sr[c][2 * q + 1])), sc2, nm2c);
-          x.x = fast_exp2(x.x);
-          x.y = fast_exp2(x.y);
-          if (q & 1) acc1 = __fadd2_rn(acc1, x); else acc0 = __fadd2_rn(acc0, x);
-          if constexpr (kExt != 0) {
-            // dropped elements leave the row sum untouched and enter P V as zeros; the factor
-            // 1 / (1 - p) is applied once, to O, in the epilogue
-            if (has_drop) {
-              const uint32_t idx = drop_row + static_cast<uint32_t>(k0 + c * 32 + 2 * q);
-              if (dropout_hash(idx, prm.ex.drop_seed) <= prm.ex.drop_threshold) x.x = 0.f;
-              if (dropout_hash(idx + 1u, prm.ex.drop_seed) <= prm.ex.drop_threshold) x.y = 0.f;
-            }
+        for (int c = 0; c < 2; ++c) {
+          // one non-blocking look at S of step t + 1 (as a rule complete by now); the answer is
+          // needed only after the exponentials, so its latency is hidden
+          if (first && c == 1 && more) s_next_ready = mbar_test_wait(bar_s_full + 2 * s + (u ^ 1), ((t + 1) >> 1) & 1);
+          // The turn is passed on after the first half (the partial row sums depend on all of its
+          // exponentials): the other tile's first half then shares the ex2 units with this tile's
+          // second half, two warps per scheduler, which hides the latencies a lone warp exposes.
+          float2 nm2c = nm2;
+          if (first && c == 1 && ping_pong) {
+            float dep = neg_ref;
+            named_barrier_arrive_mid(s ? kTurn0 : kTurn1, kTurnCount, dep, acc0.x + acc0.y, acc1.x + acc1.y);
+            nm2c = make_float2(dep, dep);  // the second half's arithmetic hangs on the arrive
           }
-          pr[c][q] = pack2<kBf16>(x.x, x.y);
+#pragma unroll
+          for (int q = 0; q < 16; ++q) {  // column pair q of the chunk
+            const float a = __uint_as_float(sr[c][2 * q]), b = __uint_as_float(sr[c][2 * q + 1]);
+            float2 x = __ffma2_rn(make_float2(a, b), sc2, nm2c);
+            x.x = fast_exp2(x.x);
+            x.y = fast_exp2(x.y);
+            if (q & 1) acc1 = __fadd2_rn(acc1, x); else acc0 = __fadd2_rn(acc0, x);
+            if (first) {
+              if (q & 1) mxb = max3(mxb, a, b); else mxa = max3(mxa, a, b);
+            }
+            if constexpr (kExt != 0) {
+              // dropped elements leave the row sum untouched and enter P V as zeros; the factor
+              // 1 / (1 - p) is applied once, to O, in the epilogue
+              if (has_drop) {
+                const uint32_t idx = drop_row + static_cast<uint32_t>(k0 + c * 32 + 2 * q);
+                if (dropout_hash(idx, prm.ex.drop_seed) <= prm.ex.drop_threshold) x.x = 0.f;
+                if (dropout_hash(idx + 1u, prm.ex.drop_seed) <= prm.ex.drop_threshold) x.y = 0.f;
+              }
+            }
+            pr[c][q] = pack2<kBf16>(x.x, x.y);
+          }
         }
+      };
+      exp_pass(neg_m, true);
+      // did a row outgrow its reference?
+      const float m_cand = fmaxf(m_run, fmaxf(mxa, mxb) * exp_scale);
+      const bool grow = m_cand - m_run > kRescaleThreshold;  // false when both are -inf (NaN)
+      float alpha = 1.f;
+      if (__any_sync(0xffffffffu, grow)) {
+        // new reference for the rows that need one; the others repeat what they had
+        const float m_new = grow ? m_cand : m_run;
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+        alpha = grow ? fast_exp2(m_run - m_use) : 1.f;
+        m_run = m_new;
+        exp_pass(-m_use, false);
       }
+      // hand the rescale factor to the correction warps
+      alpha_slot[u * 128] = alpha;
+      mbar_arrive(bar_corr + 2 * s + u);
       if ((warp & 3) == 0) trace_event(prm, s, t, 2);
       // P (two 16-bit values per column) over the first 32 columns of this step's buffer
       tmem_st16(tS, pr[0]);
@@ -366,8 +393,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       if ((warp & 3) == 0) trace_event(prm, s, t, 3);
       const float rsum = (acc0.x + acc0.y) + (acc1.x + acc1.y);
       l_run = l_run * alpha + rsum;
-      m_run = m_new;
-      if (more) finish_loads(t + 1);
+      if (more) prep_loads(t + 1);
       if ((warp & 3) == 0) trace_event(prm, s, t, 5);
     }
     s_final[s * 256 + r] = l_run;

@@ -121,62 +121,15 @@ __device__ __forceinline__ void lion_element(TP& p_io, TP g_in, TM& m_io, const 
   m_io = Elem<TM>::store(__fmaf_rn(c.c_1mb2, g, m1));
 }
 
-// The same arithmetic on two neighbouring elements at once: packed fp32 pairs (mul/add/fma.f32x2)
-// and two-at-a-time conversions halve the instruction count, which matters for all-16-bit
-// tensors (eight elements per 16-byte vector: the scalar form issues about 25 instructions per
-// 10 bytes of traffic).  Every packed operation rounds each half exactly like its scalar form.
-//
-// One shortcut: the sum t1 + t2 is not rounded to the promoted type before its sign is taken.
-// t1 and t2 are values of that type, so a non-zero sum is at least the type's smallest
-// subnormal in magnitude and cannot round to zero (nor change sign); NaN gives sign 0 either way.
-template <typename T> struct Pair;
-template <> struct Pair<float> {
-  using Packed = float2;
-  static __device__ __forceinline__ float2 load(float2 x) { return x; }
-  static __device__ __forceinline__ float2 round(float2 x) { return x; }
-  static __device__ __forceinline__ float2 store(float2 x) { return x; }
-};
-template <> struct Pair<__nv_bfloat16> {
-  using Packed = __nv_bfloat162;
-  static __device__ __forceinline__ float2 load(__nv_bfloat162 x) { return __bfloat1622float2(x); }
-  static __device__ __forceinline__ float2 round(float2 x) { return __bfloat1622float2(__float22bfloat162_rn(x)); }
-  static __device__ __forceinline__ __nv_bfloat162 store(float2 x) { return __float22bfloat162_rn(x); }
-};
-template <> struct Pair<__half> {
-  using Packed = __half2;
-  static __device__ __forceinline__ float2 load(__half2 x) { return __half22float2(x); }
-  static __device__ __forceinline__ float2 round(float2 x) { return __half22float2(__float22half2_rn(x)); }
-  static __device__ __forceinline__ __half2 store(float2 x) { return __float22half2_rn(x); }
-};
-
-__device__ __forceinline__ float sign3(float u) { return (u > 0.f) ? 1.f : ((u < 0.f) ? -1.f : 0.f); }
-
-template <typename TP, typename TM>
-__device__ __forceinline__ void lion_pair(typename Pair<TP>::Packed& p_io, typename Pair<TP>::Packed g_in,
-                                          typename Pair<TM>::Packed& m_io, const LionConsts& c) {
-  const float2 p = Pair<TP>::load(p_io);
-  const float2 g = Pair<TP>::load(g_in);
-  const float2 m = Pair<TM>::load(m_io);
-  const float2 p1 = Pair<TP>::round(__fmul2_rn(p, make_float2(c.c_wd, c.c_wd)));
-  const float2 t1 = Pair<TM>::round(__fmul2_rn(m, make_float2(c.c_b1, c.c_b1)));
-  const float2 t2 = Pair<TP>::round(__fmul2_rn(g, make_float2(c.c_1mb1, c.c_1mb1)));
-  const float2 u = __fadd2_rn(t1, t2);
-  const float2 s = make_float2(sign3(u.x), sign3(u.y));
-  p_io = Pair<TP>::store(__ffma2_rn(make_float2(c.c_nlr, c.c_nlr), s, p1));
-  const float2 m1 = Pair<TM>::round(__fmul2_rn(m, make_float2(c.c_b2, c.c_b2)));
-  m_io = Pair<TM>::store(__ffma2_rn(make_float2(c.c_1mb2, c.c_1mb2), g, m1));
-}
-
-// One 16-byte-vector group of kVec elements.
+// One 16-byte-vector group of kVec elements.  (Packed fp32 pairs, mul/add.f32x2 through the
+// __fmul2_rn / __fadd2_rn intrinsics, were tried here: no faster on all-16-bit tensors, and the
+// compiler contracted the packed multiply and add into one fused multiply-add, which flips the
+// sign of beta1*m + (1-beta1)*g where the two rounded terms cancel exactly.  The scalar _rn
+// intrinsics below are never contracted.)
 template <typename TP, typename TM>
 __device__ __forceinline__ void lion_group(Group<TP>& pv, const Group<TP>& gv, Group<TM>& mv, const LionConsts& c) {
-  using PP = typename Pair<TP>::Packed;
-  using PM = typename Pair<TM>::Packed;
-  PP* p2 = reinterpret_cast<PP*>(pv.v);
-  const PP* g2 = reinterpret_cast<const PP*>(gv.v);
-  PM* m2 = reinterpret_cast<PM*>(mv.v);
 #pragma unroll
-  for (int i = 0; i < kVec / 2; ++i) lion_pair<TP, TM>(p2[i], g2[i], m2[i], c);
+  for (int i = 0; i < kVec; ++i) lion_element<TP, TM>(pv.v[i], gv.v[i], mv.v[i], c);
 }
 
 // One chunk: `remaining` elements are left from p, g, m on (kChunk of them are this chunk's

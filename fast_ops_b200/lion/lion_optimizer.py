@@ -129,7 +129,7 @@ class Lion(Optimizer):
         defaults = {"lr": lr, "betas": betas, "weight_decay": weight_decay}
         super().__init__(params, defaults)
         self._momentum_dtype = momentum_dtype
-        self._lists: Dict[tuple, _TensorList] = {}
+        self._lists: Dict[int, tuple] = {}  # group index -> (address signature, prepared launches)
         self._pg = process_group
         self._zero = None
         if fused_gather and process_group is None:
@@ -140,6 +140,38 @@ class Lion(Optimizer):
             self._zero = _Zero1State(self, process_group, momentum_dtype, fused_gather, reduce_gradients)
 
     # -- multi-tensor path ---------------------------------------------------------------
+    @staticmethod
+    def _signature(group) -> List[int]:
+        """Addresses of every parameter and of its gradient (0 = no gradient), in order: what
+        decides whether the launches prepared for this group last step can be issued again."""
+        sig = []
+        for param in group["params"]:
+            grad = param.grad
+            sig.append(param.data_ptr())
+            sig.append(0 if grad is None else grad.data_ptr())
+        return sig
+
+    def _prepare_group(self, gi: int, group) -> list:
+        """Checks every (param, grad, exp_avg) triple of the group, creates missing momentum, and
+        returns one prepared launch (a `_TensorList`) per (device, dtype, momentum dtype)."""
+        buckets: Dict[tuple, Tuple[List[Tensor], List[Tensor], List[Tensor]]] = {}
+        for param in group["params"]:
+            grad = param.grad
+            if grad is None:
+                continue
+            state = self.state[param]
+            if "exp_avg" not in state:
+                state["exp_avg"] = torch.zeros_like(
+                    param, dtype=self._momentum_dtype or param.dtype, memory_format=torch.preserve_format)
+            exp_avg = state["exp_avg"]
+            _check_triple(param, grad, exp_avg)
+            key = (gi, param.device.index, param.dtype, exp_avg.dtype)
+            ps, gs, ms = buckets.setdefault(key, ([], [], []))
+            ps.append(param)
+            gs.append(grad)
+            ms.append(exp_avg)
+        return [_TensorList(key, ps, gs, ms) for key, (ps, gs, ms) in buckets.items()]
+
     @torch.no_grad()
     def step(self) -> None:
         """Parameter and momentum update (no closure, no return value: lion_optimizer.py:57)."""
@@ -148,43 +180,29 @@ class Lion(Optimizer):
             return
         lib = _lib.load()
         for gi, group in enumerate(self.param_groups):
-            lr = group["lr"]
-            weight_decay = group["weight_decay"]
-            beta1, beta2 = group["betas"]
-            buckets: Dict[tuple, Tuple[List[Tensor], List[Tensor], List[Tensor]]] = {}
-            for param in group["params"]:
-                grad = param.grad
-                if grad is None:
-                    continue
-                state = self.state[param]
-                if "exp_avg" not in state:
-                    state["exp_avg"] = torch.zeros_like(
-                        param, dtype=self._momentum_dtype or param.dtype, memory_format=torch.preserve_format)
-                exp_avg = state["exp_avg"]
-                _check_triple(param, grad, exp_avg)
-                key = (gi, param.device.index, param.dtype, exp_avg.dtype)
-                ps, gs, ms = buckets.setdefault(key, ([], [], []))
-                ps.append(param)
-                gs.append(grad)
-                ms.append(exp_avg)
-            for key, (ps, gs, ms) in buckets.items():
-                ptr_key = tuple(t.data_ptr() for t in ps) + tuple(t.data_ptr() for t in gs) + tuple(
-                    t.data_ptr() for t in ms)
-                tl = self._lists.get(key)
-                if tl is None or tl.key != ptr_key:
-                    tl = _TensorList(ptr_key, ps, gs, ms)
-                    self._lists[key] = tl
-                device_index = key[1]
+            # A training loop presents the same tensors step after step: while no parameter or
+            # gradient address has changed, the checks and the pointer arrays of the last step stand.
+            sig = self._signature(group)
+            cached = self._lists.get(gi)
+            if cached is None or cached[0] != sig:
+                cached = (sig, self._prepare_group(gi, group))
+                self._lists[gi] = cached
+            lr = float(group["lr"])
+            weight_decay = float(group["weight_decay"])
+            beta1, beta2 = (float(b) for b in group["betas"])
+            for tl in cached[1]:
+                _, device_index, p_dtype, m_dtype = tl.key
                 _lib.check(lib.fo_lion_multi_tensor_step(
                     tl.params, tl.grads, tl.moms, tl.numels, tl.n,
-                    _lib.dtype_code(key[2]), _lib.dtype_code(key[2]), _lib.dtype_code(key[3]),
-                    float(lr), float(beta1), float(beta2), float(weight_decay), device_index,
+                    _lib.dtype_code(p_dtype), _lib.dtype_code(p_dtype), _lib.dtype_code(m_dtype),
+                    lr, beta1, beta2, weight_decay, device_index,
                     _lib.current_stream_ptr(torch.device("cuda", device_index))))
 
     def load_state_dict(self, state_dict) -> None:
         """As torch.optim.Optimizer.load_state_dict; in process_group mode the loaded momentum
         (this rank's slices, as state_dict() saved them) is copied back into the rank's shard."""
         super().load_state_dict(state_dict)
+        self._lists.clear()  # the momentum tensors are new objects
         if self._zero is not None:
             self._zero.adopt_loaded_state()
 
