@@ -105,6 +105,10 @@ struct AttnParams {
   AttnExtras ex;  // read only by the kernel variants built for bias / dropout
   int ping_pong;  // 64-key-step kernel: the two query tiles take turns on the ex2 units (1) or not (0)
   int device;     // device index of the launch (host side only)
+  int num_sms;    // multiprocessors of that device: the size of a persistent grid
+  // Persistent kernels: two words in global memory, zero at launch, that the launch's CTAs use to
+  // hand out work items ([0]) and to find the last CTA, which zeroes them again ([1]).
+  int* sched;
 };
 
 // One element of a bias row as log2(e) * value; `base` points at column 0 of the row.

@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
@@ -12,6 +13,7 @@
 #include "flash_attn_simple.cuh"
 #include "flash_attn_ws.cuh"
 #include "flash_attn_ws64.cuh"
+#include "flash_attn_ws64p.cuh"
 #include "fo_host.h"
 #include "fo_tma.h"
 
@@ -22,6 +24,36 @@ AttnOptions g_attn_options;
 }  // namespace fo
 
 namespace {
+
+// Scheduling words of the persistent forward kernel: every launch is given one pair (round robin),
+// which its last CTA zeroes again.  Launches that run at the same time (different streams) thus
+// use different pairs unless more than kSchedSlots of them are in flight at once.
+constexpr int kSchedSlots = 1024;
+__device__ int g_attn_sched[kSchedSlots][2];
+std::atomic<unsigned> g_sched_next{0};
+
+struct DeviceInfo {
+  int* sched = nullptr;  // device address of g_attn_sched
+  int num_sms = 0;
+};
+
+// Per-device facts a launch needs, looked up once (with the device current).
+const DeviceInfo* device_info(int device) {
+  static std::mutex mu;
+  static DeviceInfo info[64];
+  if (device < 0 || device >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  DeviceInfo& d = info[device];
+  if (d.sched == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_attn_sched) != cudaSuccess || p == nullptr) return nullptr;
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n <= 0) return nullptr;
+    d.num_sms = n;
+    d.sched = static_cast<int*>(p);
+  }
+  return &d;
+}
 
 using fo::AttnParams;
 using fo::g_attn_trace;
@@ -128,7 +160,7 @@ umma_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   if (warp == 0) tmem_dealloc(tmem_base, 256);
 }
 
-enum class AttnImpl { kAuto = 0, kSimple = 1, kWarpSpecialized = 2, kWarpSpecialized64 = 3 };
+enum class AttnImpl { kAuto = 0, kSimple = 1, kWarpSpecialized = 2, kWarpSpecialized64 = 3, kPersistent64 = 4 };
 
 template <int D, bool kBf16>
 int launch_simple(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& prm,
@@ -237,6 +269,10 @@ static int attn_fwd_impl(const void* q, const void* k, const void* v, void* o, f
   prm.kv_head_bcast = kv_bcast ? 1 : 0;
   prm.ping_pong = fo::g_attn_options.ping_pong.load(std::memory_order_relaxed);
   prm.device = device;
+  const DeviceInfo* info = device_info(device);
+  if (!info) return fo::fail(FO_ERR_CUDA, "cannot look up device %d", device);
+  prm.num_sms = info->num_sms;
+  prm.sched = info->sched + 2 * (g_sched_next.fetch_add(1, std::memory_order_relaxed) % kSchedSlots);
   std::memset(&prm.ex, 0, sizeof(prm.ex));
   prm.ex.drop_rescale = 1.f;
   const bool ext = ex != nullptr && (ex->bias != nullptr || ex->dropout);
@@ -273,6 +309,10 @@ static int attn_fwd_impl(const void* q, const void* k, const void* v, void* o, f
   if (mode == M) {                                                                                     \
     if (Dk == 128) return bf16 ? fo::LAUNCH<128, true, M>(tq, tk, tv, prm, s) : fo::LAUNCH<128, false, M>(tq, tk, tv, prm, s); \
     return bf16 ? fo::LAUNCH<64, true, M>(tq, tk, tv, prm, s) : fo::LAUNCH<64, false, M>(tq, tk, tv, prm, s);                 \
+  }
+  if (impl == AttnImpl::kPersistent64) {
+    FO_WS_MODE(launch_ws64p, 0)  // plain attention only; bias and dropout run in the 64-key kernel
+    impl = AttnImpl::kWarpSpecialized64;
   }
   if (impl == AttnImpl::kWarpSpecialized64) {
     FO_WS_MODE(launch_ws64, 0)
@@ -411,7 +451,8 @@ extern "C" int fo_debug_wait_timeout(int budget_us, int* returned, int device, v
 
 extern "C" int fo_attn_configure(int impl, int ping_pong, int head_group) {
   fo::clear_error();
-  FO_REQUIRE(impl >= -1 && impl <= 3, "impl must be -1 (keep), 0 (auto), 1 (simple), 2 (128-key) or 3 (64-key)");
+  FO_REQUIRE(impl >= -1 && impl <= 4,
+             "impl must be -1 (keep), 0 (auto), 1 (simple), 2 (128-key), 3 (64-key) or 4 (64-key, persistent grid)");
   FO_REQUIRE(ping_pong >= -1 && ping_pong <= 1, "ping_pong must be -1 (keep), 0 or 1");
   FO_REQUIRE(head_group >= -1, "head_group must be -1 (keep), 0 (automatic) or a positive head count");
   if (impl >= 0) fo::g_attn_options.impl.store(impl, std::memory_order_relaxed);

@@ -175,6 +175,29 @@ __device__ __forceinline__ void named_barrier_arrive_mid(int id, int count, floa
   asm volatile("bar.arrive %1, %2;" : "+f"(dep) : "r"(id), "r"(count), "f"(a), "f"(b) : "memory");
 }
 
+// Turn-taking between two groups of warps that share an execution unit.  The operations above
+// order the barrier against arithmetic only for the compiler's front end; the assembler schedules
+// the machine code again and, since a barrier instruction has no register operands, may move pure
+// arithmetic across it.  These two tie the barrier to memory operations, which are not moved
+// across a barrier, and the arithmetic to the values those operations produce or consume:
+//   turn_wait: bar.sync, then a volatile load of a shared-memory word that holds 0.0f; the caller
+//              adds the loaded value into an operand of everything that must come after.
+//   turn_pass: a volatile store of `v` (something computed from all the work that must come first)
+//              into a private shared-memory slot, then bar.arrive.
+__device__ __forceinline__ float turn_wait(int id, int count, const float* zero_word) {
+  float v;
+  asm volatile("bar.sync %1, %2;\n\tld.volatile.shared.f32 %0, [%3];"
+               : "=f"(v)
+               : "r"(id), "r"(count), "r"(smem_u32(zero_word))
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void turn_pass(int id, int count, float* slot, float v) {
+  asm volatile("st.volatile.shared.f32 [%2], %3;\n\tbar.arrive %0, %1;"
+               ::"r"(id), "r"(count), "r"(smem_u32(slot)), "f"(v)
+               : "memory");
+}
+
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Waits until the shared-memory source of all committed stores has been read.
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }

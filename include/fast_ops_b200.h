@@ -76,7 +76,8 @@ int fo_flash_attn_fwd(const void* q, const void* k, const void* v, void* o, floa
  * Process-wide options of the attention forward (tuning and tests; nothing in the reference
  * corresponds).  Each argument: -1 leaves the option as it is.
  *   impl       : 0 = chosen per call (default), 1 = the unoverlapped bring-up kernel, 2 = the
- *                warp-specialised kernel with 128-key softmax tiles, 3 = the one with 64-key steps.
+ *                warp-specialised kernel with 128-key softmax tiles, 3 = the one with 64-key steps,
+ *                4 = the 64-key kernel as a persistent grid (plain attention only).
  *   ping_pong  : 64-key kernel: 1 (default) = the two query tiles of a CTA take turns on the
  *                exponential units, 0 = they run free.
  *   head_group : heads scheduled together so that their K and V stay in L2; 0 (default) = derived

@@ -16,7 +16,7 @@ pytestmark = pytest.mark.gpu
 
 TOL = {torch.float16: 2e-3, torch.bfloat16: 1e-2}
 LSE_TOL = 1e-3
-IMPLS = ["ws", "ws64", "simple"]
+IMPLS = ["ws", "ws64", "ws64p", "simple"]
 
 
 @pytest.fixture(params=IMPLS)
@@ -71,7 +71,7 @@ def test_attention_matches_oracle(cuda_device, impl, case):
     assert (lse - ref_lse).abs().max().item() <= LSE_TOL
 
 
-@pytest.mark.parametrize("kernel", ["ws64", "ws"])
+@pytest.mark.parametrize("kernel", ["ws64", "ws64p", "ws"])
 def test_long_context_sample_against_oracle(cuda_device, kernel):
     """S = 16384, D = 128, bf16, causal (the long-context shape) on two heads, all rows checked."""
     L.attn_configure(impl=kernel)
