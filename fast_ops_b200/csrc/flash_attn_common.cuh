@@ -141,6 +141,7 @@ constexpr int kTraceEvents = 6;
 
 __device__ __forceinline__ void trace_event(const AttnParams& prm, int role, int j, int ev) {
 #if FO_ATTN_TRACE
+  if (FO_ATTN_TRACE == 2 && (role == 2 || (ev != 0 && ev != 2))) return;  // light: softmax turn / exponentials done only
   if (prm.trace != nullptr && blockIdx.x == 0 && (threadIdx.x & 31) == 0 && j < kTraceIters)
     prm.trace[(role * kTraceIters + j) * kTraceEvents + ev] = clock64();
 #else
