@@ -550,9 +550,9 @@ def zero1_parity_check(d: Dist, flat_p, flat_g, m_shard, begin, end, step_fn, hy
         d.dist.all_reduce(hi, op=d.dist.ReduceOp.MAX)
         if int(lo.item()) != int(hi.item()):
             bad |= 4
-        flags = torch.tensor([bad], device=d.device)
-        d.dist.all_reduce(flags, op=d.dist.ReduceOp.BOR)
-        bad = int(flags.item())
+        flags = torch.tensor([bad & 1, bad & 2, bad & 4], device=d.device)  # NCCL has no bitwise OR: MAX per bit
+        d.dist.all_reduce(flags, op=d.dist.ReduceOp.MAX)
+        bad = int(flags.sum().item())
     if bad == 0:
         return "ok"
     what = [name for bit, name in ((1, "parameters differ from the oracle"), (2, "momentum differs from the oracle"),

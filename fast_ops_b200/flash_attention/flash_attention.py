@@ -50,13 +50,14 @@ def _prepare_bias(bias: Optional[Tensor], Q: Tensor, N: int):
 def next_dropout_rng(device: torch.device, count: int) -> Tuple[int, int]:
     """(seed, offset) of the device's default CUDA generator, whose offset is then advanced by
     `count` rounded up to a multiple of 4: the bookkeeping of the reference
-    (flash_attention_triton.py:641-665), so that manual_seed() followed by the same sequence of
-    calls gives the same masks."""
-    state = torch.cuda.get_rng_state(device)
-    words = state.numpy().view("uint64")  # the last two words are the seed and the offset
-    seed, offset = int(words[-2]), int(words[-1])
-    words[-1] += ((int(count) + 3) // 4) * 4
-    torch.cuda.set_rng_state(state, device)
+    (flash_attention_triton.py:641-665, which edits the last two 64-bit words of the generator's
+    state tensor: the same seed and offset), so that manual_seed() followed by the same sequence
+    of calls gives the same masks."""
+    device = torch.device(device)
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    gen = torch.cuda.default_generators[index]
+    seed, offset = int(gen.initial_seed()), int(gen.get_offset())
+    gen.set_offset(offset + ((int(count) + 3) // 4) * 4)
     return seed, offset
 
 
