@@ -612,7 +612,8 @@ def bench_lion_c5(d: Dist, steps: int, warmup: int, peaks):
            "parity_check": parity,
            "roofline": {"bound": "hbm", "achieved": shard_bytes / (ms_kernel * 1e-3) / 1e9, "peak": peaks["hbm_gbs"],
                         "unit": "GB/s", "frac": shard_bytes / (ms_kernel * 1e-3) / 1e9 / peaks["hbm_gbs"],
-                        "traffic": None, "peak_source": peaks["source"] + " copy"}}
+                        "traffic": measured_traffic("lion_c5") if not d.on else None,
+                        "peak_source": peaks["source"] + " copy"}}
     if d.on:
         recv = (d.world - 1) / d.world * total * 2
         res["all_gather"] = {"ms": ms_gather, "bus_gbs": recv / (ms_gather * 1e-3) / 1e9,
