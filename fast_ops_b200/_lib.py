@@ -96,12 +96,12 @@ def load() -> ctypes.CDLL:
         return lib
 
 
-ATTN_IMPLS = {"auto": 0, "simple": 1, "ws": 2, "ws64": 3, "ws64p": 4}
+ATTN_IMPLS = {"auto": 0, "simple": 1, "ws": 2, "ws64": 3, "ws64p": 4, "ws64s": 5}
 
 
 def attn_configure(impl=None, ping_pong=None, head_group=None) -> None:
     """Process-wide options of the attention forward (C-ABI fo_attn_configure); None leaves an
-    option unchanged.  impl: "auto" | "simple" | "ws" | "ws64" | "ws64p"; ping_pong: bool; head_group: heads
+    option unchanged.  impl: "auto" | "simple" | "ws" | "ws64" | "ws64p" | "ws64s"; ping_pong: bool; head_group: heads
     scheduled together for L2 reuse, 0 = automatic."""
     check(load().fo_attn_configure(-1 if impl is None else ATTN_IMPLS[impl],
                                    -1 if ping_pong is None else int(bool(ping_pong)),

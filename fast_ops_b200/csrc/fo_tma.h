@@ -31,10 +31,10 @@ inline EncodeTiledFn encode_fn() {
 }
 
 // Tensor map over a (B, H, S, D) tensor with element strides (sb, sh, ss, 1): dimensions are
-// listed innermost first, the box is one [128 rows x 64 columns] swizzled tile, and reads
-// past S are filled with zeros.
+// listed innermost first, the box is one [box_rows x 64 columns] swizzled tile (128 rows, or 64
+// for the half tiles of the short-sequence kernel), and reads past S are filled with zeros.
 inline int encode_tensor_map(CUtensorMap* map, const void* base, int dtype, int B, int H, int S, int D,
-                             const int64_t strides[3], const char* name) {
+                             const int64_t strides[3], const char* name, int box_rows) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return fo::fail(FO_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   FO_REQUIRE((reinterpret_cast<uintptr_t>(base) & 15) == 0, "%s must be 16-byte aligned", name);
@@ -48,7 +48,7 @@ inline int encode_tensor_map(CUtensorMap* map, const void* base, int dtype, int 
                               static_cast<cuuint64_t>(B)};
   const cuuint64_t gstrides[3] = {static_cast<cuuint64_t>(ss) * 2, static_cast<cuuint64_t>(sh) * 2,
                                   static_cast<cuuint64_t>(sb) * 2};
-  const cuuint32_t box[4] = {kBoxCols, kBlockN, 1, 1};
+  const cuuint32_t box[4] = {kBoxCols, static_cast<cuuint32_t>(box_rows), 1, 1};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
   const CUtensorMapDataType dt = dtype == FO_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   CUresult r = fn(map, dt, 4, const_cast<void*>(base), dims, gstrides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -66,10 +66,10 @@ constexpr int kTensorMapCacheSize = 16;
 struct TensorMapKey {
   const void* base;
   int64_t strides[3];
-  int dtype, B, H, S, D;
+  int dtype, B, H, S, D, box_rows;
   bool operator==(const TensorMapKey& o) const {
     return base == o.base && strides[0] == o.strides[0] && strides[1] == o.strides[1] && strides[2] == o.strides[2] &&
-           dtype == o.dtype && B == o.B && H == o.H && S == o.S && D == o.D;
+           dtype == o.dtype && B == o.B && H == o.H && S == o.S && D == o.D && box_rows == o.box_rows;
   }
 };
 
@@ -80,15 +80,15 @@ struct TensorMapCache {
 };
 
 inline int make_tensor_map(CUtensorMap* map, const void* base, int dtype, int B, int H, int S, int D,
-                           const int64_t strides[3], const char* name) {
+                           const int64_t strides[3], const char* name, int box_rows = kBlockN) {
   thread_local TensorMapCache cache;
-  const TensorMapKey key{base, {strides[0], strides[1], strides[2]}, dtype, B, H, S, D};
+  const TensorMapKey key{base, {strides[0], strides[1], strides[2]}, dtype, B, H, S, D, box_rows};
   for (int i = 0; i < cache.used; ++i)
     if (cache.keys[i] == key) {
       *map = cache.maps[i];
       return FO_OK;
     }
-  if (int rc = encode_tensor_map(map, base, dtype, B, H, S, D, strides, name)) return rc;
+  if (int rc = encode_tensor_map(map, base, dtype, B, H, S, D, strides, name, box_rows)) return rc;
   const int slot = cache.next;
   cache.keys[slot] = key;
   cache.maps[slot] = *map;

@@ -77,7 +77,8 @@ int fo_flash_attn_fwd(const void* q, const void* k, const void* v, void* o, floa
  * corresponds).  Each argument: -1 leaves the option as it is.
  *   impl       : 0 = chosen per call (default), 1 = the unoverlapped bring-up kernel, 2 = the
  *                warp-specialised kernel with 128-key softmax tiles, 3 = the one with 64-key steps,
- *                4 = the 64-key kernel as a persistent grid (plain attention only).
+ *                4 = the 64-key kernel as a persistent grid, 5 = the 64-key kernel with one query
+ *                tile per CTA and two CTAs per SM (4 and 5: plain attention only).
  *   ping_pong  : 64-key kernel: 1 (default) = the two query tiles of a CTA take turns on the
  *                exponential units, 0 = they run free.
  *   head_group : heads scheduled together so that their K and V stay in L2; 0 (default) = derived

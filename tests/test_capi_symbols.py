@@ -64,7 +64,7 @@ def test_bias_and_dropout_arguments_are_validated_without_a_gpu():
 def test_attention_options_are_validated_without_a_gpu():
     lib = L.load()
     assert lib.fo_attn_configure(-1, -1, -1) == 0  # leaves everything as it is
-    assert lib.fo_attn_configure(5, -1, -1) == -1 and b"impl" in lib.fo_last_error()
+    assert lib.fo_attn_configure(6, -1, -1) == -1 and b"impl" in lib.fo_last_error()
     assert lib.fo_attn_configure(-1, 2, -1) == -1 and b"ping_pong" in lib.fo_last_error()
     assert lib.fo_attn_configure(-1, -1, -2) == -1 and b"head_group" in lib.fo_last_error()
     L.attn_configure(impl="ws", ping_pong=False, head_group=3)

@@ -16,7 +16,7 @@ pytestmark = pytest.mark.gpu
 
 TOL = {torch.float16: 2e-3, torch.bfloat16: 1e-2}
 LSE_TOL = 1e-3
-IMPLS = ["ws", "ws64", "ws64p", "simple"]
+IMPLS = ["ws", "ws64", "ws64p", "ws64s", "simple"]
 
 
 @pytest.fixture(params=IMPLS)
