@@ -74,6 +74,8 @@ def load() -> ctypes.CDLL:
     existing library is loaded as it is, even when sources are newer: rebuild with
     `python -m fast_ops_b200.build` after editing them."""
     global _lib
+    if _lib is not None:  # the common case, without the lock
+        return _lib
     with _lock:
         if _lib is not None:
             return _lib
@@ -137,8 +139,16 @@ def dtype_code(dtype) -> int:
 
 
 def current_stream_ptr(device) -> int:
+    """Raw cudaStream_t of torch's current stream on `device` (the cheap accessor when this torch
+    has it: constructing a torch.cuda.Stream object costs a few microseconds per call)."""
     import torch
 
+    raw = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+    if raw is not None:
+        index = device.index if isinstance(device, torch.device) else int(device)
+        if index is None:
+            index = torch.cuda.current_device()
+        return raw(index)
     return torch.cuda.current_stream(device).cuda_stream
 
 

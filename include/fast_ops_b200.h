@@ -179,9 +179,14 @@ int fo_lion_update(void* param, const void* grad, void* exp_avg, int64_t numel,
  * per-tensor loop of Lion.step() (fast_ops/lion/lion_optimizer.py:57-76).
  * `params`, `grads`, `exp_avgs` and `numels` are HOST arrays of n_tensors
  * entries holding device pointers / element counts.  The device-side tensor
- * table is built on the first call for a given list and cached inside the
- * library (keyed by the list's contents), so later calls with the same list
- * do no host-to-device copy.
+ * table is built on the first call for a given list (cudaMalloc, and a copy on
+ * `stream`) and cached inside the library, keyed by the list's contents, so
+ * later calls with the same list do no host-to-device copy.  At most 32 lists
+ * are kept; the least recently used one is dropped for a new one.  A list of
+ * one tensor needs no table.  CUDA graphs: a captured launch keeps its list's
+ * table, so make the first call with a list outside the capture (on a capturing
+ * stream it is refused with FO_ERR_UNSUPPORTED), and neither 32 other lists nor
+ * fo_lion_clear_cache may come between the capture and a replay.
  */
 int fo_lion_multi_tensor_step(void* const* params, const void* const* grads,
                               void* const* exp_avgs, const int64_t* numels, int n_tensors,
