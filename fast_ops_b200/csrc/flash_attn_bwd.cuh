@@ -19,9 +19,14 @@
 //
 // Warps 0-7: two threads per query row, each taking half of the tile's columns (no reduction
 // across a row is needed in the backward), and in the epilogue one thread per key row for dK
-// (warps 0-3) and dV (warps 4-7); warp 8 issues the MMAs; warp 9 issues the TMA loads.  The steps
-// of a query tile run in order; the load of the next Q / dO tile and the drain of the previous
-// dQ reduction overlap them.
+// (warps 0-3) and dV (warps 4-7); warp 8 issues the MMAs; warp 9 issues the TMA loads.
+//
+// The hand-offs of one query tile are split so that each side works while the other does:
+// S and dP are committed separately (the exponentials of S run under the dP matmul), P and dS are
+// handed over separately (the dV matmul runs while dS is formed and stored), and the S / dP columns
+// are released as soon as dQ sits in registers (the S matmul of the next tile runs while dQ is
+// staged and reduced).  The load of the next Q / dO tile and the drain of the previous dQ reduction
+// overlap the rest.
 #pragma once
 
 #include "flash_attn_common.cuh"
@@ -68,7 +73,7 @@ struct BwdConfig {
   static constexpr int kOffP = 4 * kTileBytes;
   static constexpr int kOffDS = kOffP + kPBytes;
   static constexpr int kOffBars = kOffDS + kPBytes;
-  static constexpr int kNumBars = 7;
+  static constexpr int kNumBars = 9;
   static constexpr int kOffMisc = kOffBars + kNumBars * 8;
   // [128] float: a row-independent bias of this key tile; read as float4, so 16-byte aligned
   static constexpr int kOffBias = (kOffMisc + 64 + 15) & ~15;
@@ -109,10 +114,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint64_t* bar_kv = bars + 0;        // TMA -> MMA: K and V of this CTA are in shared memory
   uint64_t* bar_q_full = bars + 1;    // TMA -> MMA: Q_i and dO_i loaded
   uint64_t* bar_q_empty = bars + 2;   // MMA -> TMA: every MMA reading Q_i / dO_i has completed
-  uint64_t* bar_s_full = bars + 3;    // MMA -> threads: S and dP are in tensor memory
-  uint64_t* bar_pds_full = bars + 4;  // threads -> MMA: P and dS are in shared memory (256 arrivals)
-  uint64_t* bar_dq_full = bars + 5;   // MMA -> threads: dQ tile (and dK, dV so far) complete
-  uint64_t* bar_s_free = bars + 6;    // threads -> MMA: dQ read, S / dP columns reusable (256 arrivals)
+  uint64_t* bar_s_full = bars + 3;    // MMA -> threads: S is in tensor memory
+  uint64_t* bar_dp_full = bars + 4;   // MMA -> threads: dP is in tensor memory
+  uint64_t* bar_p_full = bars + 5;    // threads -> MMA: P is in shared memory (256 arrivals)
+  uint64_t* bar_ds_full = bars + 6;   // threads -> MMA: dS is in shared memory, dP has been read (256 arrivals)
+  uint64_t* bar_dq_full = bars + 7;   // MMA -> threads: dQ tile (and dK, dV so far) complete
+  uint64_t* bar_s_free = bars + 8;    // threads -> MMA: dQ read, S / dP columns reusable (256 arrivals)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::kOffMisc);
   volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* skip = cta_abort + 1;
@@ -139,7 +146,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     mbar_init(bar_q_full, 1);
     mbar_init(bar_q_empty, 1);
     mbar_init(bar_s_full, 1);
-    mbar_init(bar_pds_full, 256);
+    mbar_init(bar_dp_full, 1);
+    mbar_init(bar_p_full, 256);
+    mbar_init(bar_ds_full, 256);
     mbar_init(bar_dq_full, 1);
     mbar_init(bar_s_free, 256);
     fence_mbar_init();
@@ -231,24 +240,21 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_wait(bar_s_full, it & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_MMA);
       tcgen05_fence_after_sync();
       if (warp == 0) bwd_trace(prm, 0, it, 0);
-      // P and dS of this thread's 64 columns, kept in registers (packed 16-bit) until the shared
-      // buffers are free
-      uint32_t pp[2][16], dd[2][16];
-      const float neg_delta_scale = -delta * prm.scale;
+      // ---- P = exp2(S * scale - LSE) of this thread's 64 columns, in fp32 registers; the dP matmul runs meanwhile ----
+      uint32_t sr[2][32];
+      tmem_ld32(tS + (half * 2) * 32, sr[0]);
+      tmem_ld32(tS + (half * 2 + 1) * 32, sr[1]);
+      uint32_t keep[2] = {0xffffffffu, 0xffffffffu};  // dropout: bit x of keep[cc] = element kept
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
         const int c = half * 2 + cc;
-        uint32_t sr[32], dpr[32];
-        tmem_ld32(tS + c * 32, sr);
-        tmem_ld32(tDP + c * 32, dpr);
         float bb[kExt ? 32 : 1];  // matrix bias only: fetched while the tensor-memory loads fly
         if constexpr (kExt) {
           if (has_bias && !vec_bias) load_bias32<kBf16>(prm.ex, bias_row, k0 + c * 32, prm.Sk, bb);
         }
-        tmem_ld_wait(sr);
-        tmem_ld_wait(dpr);
-        // P in place over the S registers; the mask (rare: diagonal and ragged tiles) is a
-        // separate, warp-uniform branch so that full tiles pay nothing for it
+        tmem_ld_wait(sr[cc]);
+        // the mask (rare: diagonal and ragged tiles) is a separate, warp-uniform branch so that
+        // full tiles pay nothing for it
         bool plain = true;
         if constexpr (kExt) {
           if (vec_bias) {
@@ -256,96 +262,134 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
             for (int x = 0; x < 32; x += 4) {
               const float4 t = *reinterpret_cast<const float4*>(sb + c * 32 + x);  // broadcast read
-              sr[x + 0] = __float_as_uint(fast_exp2(fmaf(__uint_as_float(sr[x + 0]), prm.scale_log2, t.x) - lse2));
-              sr[x + 1] = __float_as_uint(fast_exp2(fmaf(__uint_as_float(sr[x + 1]), prm.scale_log2, t.y) - lse2));
-              sr[x + 2] = __float_as_uint(fast_exp2(fmaf(__uint_as_float(sr[x + 2]), prm.scale_log2, t.z) - lse2));
-              sr[x + 3] = __float_as_uint(fast_exp2(fmaf(__uint_as_float(sr[x + 3]), prm.scale_log2, t.w) - lse2));
+              sr[cc][x + 0] = __float_as_uint(fast_exp2(fmaf(__uint_as_float(sr[cc][x + 0]), prm.scale_log2, t.x) - lse2));
+              sr[cc][x + 1] = __float_as_uint(fast_exp2(fmaf(__uint_as_float(sr[cc][x + 1]), prm.scale_log2, t.y) - lse2));
+              sr[cc][x + 2] = __float_as_uint(fast_exp2(fmaf(__uint_as_float(sr[cc][x + 2]), prm.scale_log2, t.z) - lse2));
+              sr[cc][x + 3] = __float_as_uint(fast_exp2(fmaf(__uint_as_float(sr[cc][x + 3]), prm.scale_log2, t.w) - lse2));
             }
           } else if (has_bias) {
             plain = false;
 #pragma unroll
             for (int x = 0; x < 32; ++x)
-              sr[x] = __float_as_uint(fast_exp2(fmaf(__uint_as_float(sr[x]), prm.scale_log2, bb[x]) - lse2));
+              sr[cc][x] = __float_as_uint(fast_exp2(fmaf(__uint_as_float(sr[cc][x]), prm.scale_log2, bb[x]) - lse2));
           }
         }
         if (plain) {
 #pragma unroll
           for (int x = 0; x < 32; ++x)
-            sr[x] = __float_as_uint(fast_exp2(fmaf(__uint_as_float(sr[x]), prm.scale_log2, -lse2)));
+            sr[cc][x] = __float_as_uint(fast_exp2(fmaf(__uint_as_float(sr[cc][x]), prm.scale_log2, -lse2)));
         }
         if (need_mask) {
 #pragma unroll
           for (int x = 0; x < 32; ++x) {
             const int col = k0 + c * 32 + x;
-            if (col >= prm.Sk || (prm.causal && col > row)) sr[x] = 0u;
+            if (col >= prm.Sk || (prm.causal && col > row)) sr[cc][x] = 0u;
           }
         }
+        if constexpr (kExt) {
+          if (has_drop) {
+            uint32_t kb = 0;
 #pragma unroll
-        for (int x = 0; x < 32; x += 2) {
-          const float p0 = __uint_as_float(sr[x]), p1 = __uint_as_float(sr[x + 1]);
-          float z0 = p0, z1 = p1;  // P as it enters dV: zero where the forward dropped the element
-          float g0 = __uint_as_float(dpr[x]), g1 = __uint_as_float(dpr[x + 1]);
-          if constexpr (kExt) {
-            if (has_drop) {
+            for (int x = 0; x < 32; ++x) {
               const uint32_t idx = drop_row + static_cast<uint32_t>(k0 + c * 32 + x);
-              if (dropout_hash(idx, prm.ex.drop_seed) <= prm.ex.drop_threshold) { z0 = 0.f; g0 = 0.f; }
-              if (dropout_hash(idx + 1u, prm.ex.drop_seed) <= prm.ex.drop_threshold) { z1 = 0.f; g1 = 0.f; }
+              if (dropout_hash(idx, prm.ex.drop_seed) > prm.ex.drop_threshold) kb |= 1u << x;
             }
+            keep[cc] = kb;
           }
-          // dS = P * (dP - delta) * scale, dP = 0 for a dropped element
-          const float d0 = p0 * fmaf(g0, dp_scale, neg_delta_scale);
-          const float d1 = p1 * fmaf(g1, dp_scale, neg_delta_scale);
-          pp[cc][x >> 1] = pack2<kBf16>(z0, z1);
-          dd[cc][x >> 1] = pack2<kBf16>(d0, d1);
         }
       }
       if (warp == 0) bwd_trace(prm, 0, it, 4);
       // The P / dS buffers double as the staging area of the previous tile's dQ reduction, whose
-      // shared-memory reads take a few thousand cycles: they must have finished before the
-      // buffers are overwritten, which is why the arithmetic above runs first.
+      // shared-memory reads take a while: they must have finished before the buffers are
+      // overwritten, which is why the exponentials above run first.
       if (it > 0) {
         if (tid == 0) tma_store_wait_read();
         named_barrier_sync(1, 256);
       }
+      // ---- P (zero where the forward dropped the element) -> shared memory; the dV matmul may start ----
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
         const int c = half * 2 + cc;
+        uint32_t pp[16];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          store_swizzled_unit(sP, r, c * 4 + u,
-                              make_uint4(pp[cc][4 * u], pp[cc][4 * u + 1], pp[cc][4 * u + 2], pp[cc][4 * u + 3]));
-          store_swizzled_unit(sDS, r, c * 4 + u,
-                              make_uint4(dd[cc][4 * u], dd[cc][4 * u + 1], dd[cc][4 * u + 2], dd[cc][4 * u + 3]));
+        for (int x = 0; x < 32; x += 2) {
+          float z0 = __uint_as_float(sr[cc][x]), z1 = __uint_as_float(sr[cc][x + 1]);
+          if constexpr (kExt) {
+            if (has_drop) {
+              if (!((keep[cc] >> x) & 1u)) z0 = 0.f;
+              if (!((keep[cc] >> (x + 1)) & 1u)) z1 = 0.f;
+            }
+          }
+          pp[x >> 1] = pack2<kBf16>(z0, z1);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          store_swizzled_unit(sP, r, c * 4 + u, make_uint4(pp[4 * u], pp[4 * u + 1], pp[4 * u + 2], pp[4 * u + 3]));
+      }
+      fence_proxy_async_smem();  // shared-memory writes of these threads must be visible to the tensor core's reads
+      mbar_arrive(bar_p_full);
+      if (warp == 0) bwd_trace(prm, 0, it, 5);
+
+      // ---- dS = P o (dP - delta) * scale, dP = 0 for a dropped element -> shared memory ----
+      mbar_wait(bar_dp_full, it & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_MMA);
+      tcgen05_fence_after_sync();
+      const float neg_delta_scale = -delta * prm.scale;
+      {
+        uint32_t dpr[2][32];
+        tmem_ld32(tDP + (half * 2) * 32, dpr[0]);
+        tmem_ld32(tDP + (half * 2 + 1) * 32, dpr[1]);
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+          const int c = half * 2 + cc;
+          tmem_ld_wait(dpr[cc]);
+          uint32_t dd[16];
+#pragma unroll
+          for (int x = 0; x < 32; x += 2) {
+            float g0 = __uint_as_float(dpr[cc][x]), g1 = __uint_as_float(dpr[cc][x + 1]);
+            if constexpr (kExt) {
+              if (has_drop) {
+                if (!((keep[cc] >> x) & 1u)) g0 = 0.f;
+                if (!((keep[cc] >> (x + 1)) & 1u)) g1 = 0.f;
+              }
+            }
+            const float d0 = __uint_as_float(sr[cc][x]) * fmaf(g0, dp_scale, neg_delta_scale);
+            const float d1 = __uint_as_float(sr[cc][x + 1]) * fmaf(g1, dp_scale, neg_delta_scale);
+            dd[x >> 1] = pack2<kBf16>(d0, d1);
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            store_swizzled_unit(sDS, r, c * 4 + u, make_uint4(dd[4 * u], dd[4 * u + 1], dd[4 * u + 2], dd[4 * u + 3]));
         }
       }
-      // shared-memory writes of these threads must be visible to the tensor core's reads
       fence_proxy_async_smem();
-      if (warp == 0) bwd_trace(prm, 0, it, 5);
-      tcgen05_fence_before_sync();
-      mbar_arrive(bar_pds_full);
+      tcgen05_fence_before_sync();  // the dP loads above precede the next tile's dP matmul
+      mbar_arrive(bar_ds_full);
       if (warp == 0) bwd_trace(prm, 0, it, 1);
 
       // dQ tile of this (query tile, key tile) pair -> fp32 accumulation buffer
       mbar_wait(bar_dq_full, it & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_MMA);
       tcgen05_fence_after_sync();
       if (warp == 0) bwd_trace(prm, 0, it, 2);
-      // stage the fp32 tile in shared memory (over P and dS, which the MMAs have finished
-      // reading) as D/32 swizzled boxes of [128 rows x 32 floats], then add it into the global
+      // dQ into registers first: the S / dP columns are then free for the next tile's matmuls, which
+      // run while this tile is staged in shared memory (over P and dS, which the MMAs have finished
+      // reading) as D/32 swizzled boxes of [128 rows x 32 floats] and added into the global
       // accumulation buffer with tiled bulk reductions; rows past Sq are dropped by the hardware
+      uint32_t qr[D / 64][32];
+#pragma unroll
+      for (int cc = 0; cc < D / 64; ++cc) tmem_ld32(tS + (half * (D / 64) + cc) * 32, qr[cc]);
+#pragma unroll
+      for (int cc = 0; cc < D / 64; ++cc) tmem_ld_wait(qr[cc]);
+      tcgen05_fence_before_sync();
+      mbar_arrive(bar_s_free);
 #pragma unroll
       for (int cc = 0; cc < D / 64; ++cc) {
         const int c = half * (D / 64) + cc;
-        uint32_t qr[32];
-        tmem_ld32(tS + c * 32, qr);
-        tmem_ld_wait(qr);
 #pragma unroll
         for (int u = 0; u < 8; ++u)
           *reinterpret_cast<uint4*>(sP + c * kBoxBytes + r * 128 + ((u ^ (r & 7)) * 16)) =
-              make_uint4(qr[4 * u], qr[4 * u + 1], qr[4 * u + 2], qr[4 * u + 3]);
+              make_uint4(qr[cc][4 * u], qr[cc][4 * u + 1], qr[cc][4 * u + 2], qr[cc][4 * u + 3]);
       }
       fence_proxy_async_smem();
-      tcgen05_fence_before_sync();
-      mbar_arrive(bar_s_free);
       if (warp == 0) bwd_trace(prm, 0, it, 3);
       named_barrier_sync(1, 256);
       if (tid == 0) {
@@ -420,24 +464,27 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (it > 0) mbar_wait(bar_s_free, (it - 1) & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_SOFTMAX);
       tcgen05_fence_after_sync();
 #pragma unroll
-      for (int kk = 0; kk < D / 16; ++kk) {  // S = Q K^T, dP = dO V^T  (K = head_dim)
+      for (int kk = 0; kk < D / 16; ++kk) {  // S = Q K^T  (K = head_dim)
         const uint32_t off = (kk >> 2) * kBoxStep + (kk & 3) * 2;
         umma_ss_lo_elect(tS, q_k + off, k_k + off, idesc_s, kk > 0 ? 1u : 0u);
       }
+      tcgen05_commit_elect(bar_s_full);
 #pragma unroll
-      for (int kk = 0; kk < D / 16; ++kk) {
+      for (int kk = 0; kk < D / 16; ++kk) {  // dP = dO V^T
         const uint32_t off = (kk >> 2) * kBoxStep + (kk & 3) * 2;
         umma_ss_lo_elect(tDP, do_k + off, v_k + off, idesc_s, kk > 0 ? 1u : 0u);
       }
-      tcgen05_commit_elect(bar_s_full);
+      tcgen05_commit_elect(bar_dp_full);
       bwd_trace(prm, 2, it, 1);
 
-      mbar_wait(bar_pds_full, it & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_SOFTMAX);
+      mbar_wait(bar_p_full, it & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_SOFTMAX);
       tcgen05_fence_after_sync();
       bwd_trace(prm, 2, it, 2);
 #pragma unroll
       for (int kk = 0; kk < kBlockM / 16; ++kk)  // dV += P^T dO  (K = 16 query rows per step: 2048 bytes)
         umma_ss_lo_elect(tDV, p_m + kk * 128, do_n + kk * 128, idesc_t, (it > 0 || kk > 0) ? 1u : 0u);
+      mbar_wait(bar_ds_full, it & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_SOFTMAX);
+      tcgen05_fence_after_sync();
 #pragma unroll
       for (int kk = 0; kk < kBlockM / 16; ++kk)  // dK += dS^T Q
         umma_ss_lo_elect(tDK, ds_m + kk * 128, q_n + kk * 128, idesc_t, (it > 0 || kk > 0) ? 1u : 0u);
