@@ -207,6 +207,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         named_barrier_sync(1, 256);
       }
     }
+    // LSE and delta of a row are fetched one query tile ahead, so that their latency is not in the tile's chain
+    const float* const lse_bh = prm.lse + static_cast<int64_t>(bh) * prm.Sq;
+    const float* const delta_bh = prm.delta + static_cast<int64_t>(bh) * prm.Sq;
+    float lse_next = INFINITY, delta_next = 0.f;
+    if (n_iter > 0 && i0 * kBlockM + r < prm.Sq) {
+      lse_next = lse_bh[i0 * kBlockM + r];
+      delta_next = delta_bh[i0 * kBlockM + r];
+    }
     for (int it = 0; it < n_iter; ++it) {
       const int i = i0 + it;
       const int q0 = i * kBlockM;
@@ -214,7 +222,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const bool row_ok = row < prm.Sq;
       // a row past the end, or one whose keys are all masked (LSE = -inf), gets LSE = +inf, so
       // that its P and dS are exactly 0
-      const float lse_nat = row_ok ? prm.lse[static_cast<int64_t>(bh) * prm.Sq + row] : INFINITY;
+      const float lse_nat = lse_next;
+      const float delta = delta_next;
+      if (it + 1 < n_iter && row + kBlockM < prm.Sq) {
+        lse_next = lse_bh[row + kBlockM];
+        delta_next = delta_bh[row + kBlockM];
+      } else {
+        lse_next = INFINITY;
+        delta_next = 0.f;
+      }
       const float lse2 = (lse_nat == -INFINITY) ? INFINITY : lse_nat * 1.4426950408889634f;
       const uint8_t* bias_row = nullptr;
       uint32_t drop_row = 0;
@@ -226,7 +242,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         drop_row = prm.ex.drop_base + static_cast<uint32_t>(bh) * static_cast<uint32_t>(prm.Sq) * static_cast<uint32_t>(prm.Sk) +
                    static_cast<uint32_t>(row) * static_cast<uint32_t>(prm.Sk);
       }
-      const float delta = row_ok ? prm.delta[static_cast<int64_t>(bh) * prm.Sq + row] : 0.f;
       const bool need_mask = (k0 + kBlockN > prm.Sk) || (prm.causal && k0 + kBlockN - 1 > q0);
       if constexpr (kExt) {
         // matrix bias: ask for this thread's 64 columns of the next query tile's row now
@@ -299,70 +314,60 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
       }
       if (warp == 0) bwd_trace(prm, 0, it, 4);
+      // ---- P (zero where the forward dropped the element) and dS = P o (dP - delta) * scale (dP = 0 for a
+      // dropped element), packed to 16 bits in registers ----
+      uint32_t pp[2][16], dd[2][16];
+      mbar_wait(bar_dp_full, it & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_MMA);
+      tcgen05_fence_after_sync();
+      const float neg_delta_scale = -delta * prm.scale;
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        uint32_t dpr[32];
+        tmem_ld32(tDP + (half * 2 + cc) * 32, dpr);
+        tmem_ld_wait(dpr);
+#pragma unroll
+        for (int x = 0; x < 32; x += 2) {
+          const float p0 = __uint_as_float(sr[cc][x]), p1 = __uint_as_float(sr[cc][x + 1]);
+          float z0 = p0, z1 = p1;
+          float g0 = __uint_as_float(dpr[x]), g1 = __uint_as_float(dpr[x + 1]);
+          if constexpr (kExt) {
+            if (has_drop) {
+              if (!((keep[cc] >> x) & 1u)) { z0 = 0.f; g0 = 0.f; }
+              if (!((keep[cc] >> (x + 1)) & 1u)) { z1 = 0.f; g1 = 0.f; }
+            }
+          }
+          pp[cc][x >> 1] = pack2<kBf16>(z0, z1);
+          dd[cc][x >> 1] = pack2<kBf16>(p0 * fmaf(g0, dp_scale, neg_delta_scale), p1 * fmaf(g1, dp_scale, neg_delta_scale));
+        }
+      }
+      tcgen05_fence_before_sync();  // the dP loads above precede the next tile's dP matmul
       // The P / dS buffers double as the staging area of the previous tile's dQ reduction, whose
-      // shared-memory reads take a while: they must have finished before the buffers are
-      // overwritten, which is why the exponentials above run first.
+      // shared-memory reads take about 2800 cycles: they must have finished before the buffers are
+      // overwritten, which is why all of the arithmetic above runs first.
       if (it > 0) {
         if (tid == 0) tma_store_wait_read();
         named_barrier_sync(1, 256);
       }
-      // ---- P (zero where the forward dropped the element) -> shared memory; the dV matmul may start ----
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
         const int c = half * 2 + cc;
-        uint32_t pp[16];
-#pragma unroll
-        for (int x = 0; x < 32; x += 2) {
-          float z0 = __uint_as_float(sr[cc][x]), z1 = __uint_as_float(sr[cc][x + 1]);
-          if constexpr (kExt) {
-            if (has_drop) {
-              if (!((keep[cc] >> x) & 1u)) z0 = 0.f;
-              if (!((keep[cc] >> (x + 1)) & 1u)) z1 = 0.f;
-            }
-          }
-          pp[x >> 1] = pack2<kBf16>(z0, z1);
-        }
 #pragma unroll
         for (int u = 0; u < 4; ++u)
-          store_swizzled_unit(sP, r, c * 4 + u, make_uint4(pp[4 * u], pp[4 * u + 1], pp[4 * u + 2], pp[4 * u + 3]));
+          store_swizzled_unit(sP, r, c * 4 + u,
+                              make_uint4(pp[cc][4 * u], pp[cc][4 * u + 1], pp[cc][4 * u + 2], pp[cc][4 * u + 3]));
       }
       fence_proxy_async_smem();  // shared-memory writes of these threads must be visible to the tensor core's reads
-      mbar_arrive(bar_p_full);
+      mbar_arrive(bar_p_full);   // the dV matmul runs while dS is stored
       if (warp == 0) bwd_trace(prm, 0, it, 5);
-
-      // ---- dS = P o (dP - delta) * scale, dP = 0 for a dropped element -> shared memory ----
-      mbar_wait(bar_dp_full, it & 1, cta_abort, dstat, FO_STATUS_TIMEOUT_MMA);
-      tcgen05_fence_after_sync();
-      const float neg_delta_scale = -delta * prm.scale;
-      {
-        uint32_t dpr[2][32];
-        tmem_ld32(tDP + (half * 2) * 32, dpr[0]);
-        tmem_ld32(tDP + (half * 2 + 1) * 32, dpr[1]);
 #pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
-          const int c = half * 2 + cc;
-          tmem_ld_wait(dpr[cc]);
-          uint32_t dd[16];
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = half * 2 + cc;
 #pragma unroll
-          for (int x = 0; x < 32; x += 2) {
-            float g0 = __uint_as_float(dpr[cc][x]), g1 = __uint_as_float(dpr[cc][x + 1]);
-            if constexpr (kExt) {
-              if (has_drop) {
-                if (!((keep[cc] >> x) & 1u)) g0 = 0.f;
-                if (!((keep[cc] >> (x + 1)) & 1u)) g1 = 0.f;
-              }
-            }
-            const float d0 = __uint_as_float(sr[cc][x]) * fmaf(g0, dp_scale, neg_delta_scale);
-            const float d1 = __uint_as_float(sr[cc][x + 1]) * fmaf(g1, dp_scale, neg_delta_scale);
-            dd[x >> 1] = pack2<kBf16>(d0, d1);
-          }
-#pragma unroll
-          for (int u = 0; u < 4; ++u)
-            store_swizzled_unit(sDS, r, c * 4 + u, make_uint4(dd[4 * u], dd[4 * u + 1], dd[4 * u + 2], dd[4 * u + 3]));
-        }
+        for (int u = 0; u < 4; ++u)
+          store_swizzled_unit(sDS, r, c * 4 + u,
+                              make_uint4(dd[cc][4 * u], dd[cc][4 * u + 1], dd[cc][4 * u + 2], dd[cc][4 * u + 3]));
       }
       fence_proxy_async_smem();
-      tcgen05_fence_before_sync();  // the dP loads above precede the next tile's dP matmul
       mbar_arrive(bar_ds_full);
       if (warp == 0) bwd_trace(prm, 0, it, 1);
 
