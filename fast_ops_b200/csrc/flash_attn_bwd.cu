@@ -68,11 +68,11 @@ attn_bwd_finish_dq_kernel(const float* __restrict__ dq_accum, uint16_t* __restri
 template <int D, bool kBf16, int kExt>
 int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
                const CUtensorMap& tdq, const fo::AttnBwdParams& prm, cudaStream_t stream) {
+  dim3 grid((prm.Sk + fo::kBlockN - 1) / fo::kBlockN, prm.B * prm.H);
   auto kernel = fo::attn_bwd_kernel<D, kBf16, kExt>;
   constexpr int smem = fo::BwdConfig<D>::kSmemBytes;
   FO_CUDA_CHECK((fo::ensure_dynamic_smem<fo::attn_bwd_kernel<D, kBf16, kExt>>(smem, prm.device)));
-  dim3 grid((prm.Sk + fo::kBlockN - 1) / fo::kBlockN, prm.B * prm.H);
-  kernel<<<grid, 320, smem, stream>>>(tq, tk, tv, tdo, tdq, prm);
+  kernel<<<grid, 512, smem, stream>>>(tq, tk, tv, tdo, tdq, prm);
   fo::g_launch_count.fetch_add(1, std::memory_order_relaxed);
   FO_CUDA_CHECK(cudaGetLastError());
   return FO_OK;

@@ -50,12 +50,6 @@ constexpr float kRescaleThreshold = 8.0f;
 
 
 
-template <int kRegs> __device__ __forceinline__ void reg_alloc() {
-  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs));
-}
-template <int kRegs> __device__ __forceinline__ void reg_dealloc() {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs));
-}
 
 // grid = (num_q_pairs * B * H); block = 512.  Consecutive blocks sweep a group of heads whose K
 // and V fit in L2 together, so the query tiles of those heads re-read K/V from L2 rather than
