@@ -173,13 +173,14 @@ __device__ __forceinline__ bool all_aligned16(const void* a, const void* b, cons
   return ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c)) & 15) == 0;
 }
 
-// One launch covers all tensors.  `chunk_start[t]` is the index of tensor t's first
-// chunk in the global chunk numbering (chunk_start[n_tensors] = total).  CTAs stride
-// over chunks; because a CTA's chunk index only grows, it finds the owning tensor by
-// walking `t` forward from where the previous chunk left it.
+// One launch covers all tensors, described by a table of one entry per TENSOR (the form the
+// allocation-free entry point can keep in a fixed device array).  `chunk_start[t]` is the index
+// of tensor t's first chunk in the global chunk numbering (chunk_start[n_tensors] = total).  A
+// resident wave of CTAs strides over the chunks; because a CTA's chunk index only grows, it finds
+// the owning tensor by walking `t` forward from where the previous chunk left it.
 template <typename TP, typename TM>
 __global__ void __launch_bounds__(kThreads)
-lion_multi_tensor_kernel(const LionTensor* __restrict__ tensors,
+lion_table_walk_kernel(const LionTensor* __restrict__ tensors,
                          const int64_t* __restrict__ chunk_start, int n_tensors,
                          int64_t total_chunks, LionConsts c) {
   int t = 0;
@@ -207,24 +208,63 @@ lion_multi_tensor_kernel(const LionTensor* __restrict__ tensors,
 // The same step on ONE tensor, described by the kernel's own arguments: no device table, so
 // nothing is allocated, copied or cached for it (the per-tensor call of the reference's
 // optimizer loop, and a ZeRO-1 shard, come through here).
-// Groups per thread and chunk in the single-tensor kernel.  Measured on 6.7e9 bf16 elements
-// (p, g, m all 16-bit): 2 groups 5.73 TB/s, 4 groups 6.15, 6 groups 6.20, 8 groups 3.85 (the
-// registers of 24 vectors in flight cost more occupancy than the loads gain).
-template <typename TP, typename TM>
-struct SingleUnroll {
-  static constexpr int value = kUnroll;
-};
+// One 16-byte group per thread and array, and one CTA per 2048 elements instead of a resident
+// wave that loops.  Measured on 6.7e9 bf16 elements (p, g, m all 16-bit), TB/s: a resident wave
+// with 2 / 4 / 6 / 8 groups per thread 5.73 / 6.15 / 6.20 / 3.85; one CTA per chunk with
+// 1 / 2 / 3 / 4 / 8 groups 7.01 / 7.03 / 6.59 / 6.80 / 4.40 (a torch elementwise add over three
+// arrays of that size moves 7.08, a copy 6.59).  The multi-tensor kernel keeps its resident wave:
+// with more CTAs each of them walks further through the tensor table (6.61 TB/s on the
+// GPT-2-medium list with one wave, 6.56 with four, 6.05 with sixteen).
+constexpr int kSingleUnroll = 1;
 
 template <typename TP, typename TM>
 __global__ void __launch_bounds__(kThreads)
 lion_single_tensor_kernel(TP* __restrict__ p, const TP* __restrict__ g, TM* __restrict__ m, int64_t numel,
                           int64_t total_chunks, LionConsts c) {
-  constexpr int kU = SingleUnroll<TP, TM>::value;
+  constexpr int kU = kSingleUnroll;
   constexpr int kElems = kThreads * kVec * kU;
   const bool aligned = all_aligned16(p, g, m);
   for (int64_t chunk = blockIdx.x; chunk < total_chunks; chunk += gridDim.x) {
     const int64_t base = chunk * kElems;
     lion_chunk<TP, TM, kU>(p + base, g + base, m + base, numel - base, aligned, c);
+  }
+}
+
+// One launch covers all tensors, described by one record per CHUNK of kChunk elements (pointers
+// already advanced to the chunk, and how many elements are left of its tensor from there on): a
+// CTA needs one 32-byte load to know its work, so the launch can use one CTA per quarter chunk
+// like the single-tensor kernel instead of a resident wave that walks a tensor table.  The
+// records cost 32 bytes of device memory and of traffic per kChunk elements (0.05 % of the
+// step's traffic with 16-bit tensors).
+struct ChunkRecord {
+  void* p;
+  const void* g;
+  void* m;
+  int64_t remaining;
+};
+static_assert(sizeof(ChunkRecord) == 32, "two 16-byte loads");
+
+// One group per thread, as in the single-tensor kernel.  Measured, one CTA per 2048 / 4096 / 8192
+// elements: GPT-2-medium list (fp32 p, g) 6.94 / 6.83 / 6.89 TB/s, a list of 64 bf16 matrices of
+// 4096 x 11008 6.39 / 6.65 / 6.50.
+constexpr int kMultiUnroll = 1;
+constexpr int kSubElems = kThreads * kVec * kMultiUnroll;  // elements of one CTA
+constexpr int kSubsPerChunk = kChunk / kSubElems;
+static_assert(kChunk % kSubElems == 0 && kSubElems % 8 == 0, "a CTA's part starts 16-byte aligned whenever the tensor does");
+
+template <typename TP, typename TM>
+__global__ void __launch_bounds__(kThreads)
+lion_multi_tensor_kernel(const ChunkRecord* __restrict__ records, int64_t total_subs, LionConsts c) {
+  for (int64_t sub = blockIdx.x; sub < total_subs; sub += gridDim.x) {
+    const uint4* rp = reinterpret_cast<const uint4*>(records + sub / kSubsPerChunk);
+    const uint4 lo = __ldg(rp), hi = __ldg(rp + 1);
+    ChunkRecord r;
+    memcpy(&r, &lo, 16);
+    memcpy(reinterpret_cast<char*>(&r) + 16, &hi, 16);
+    const int64_t off = (sub % kSubsPerChunk) * static_cast<int64_t>(kSubElems);
+    if (off >= r.remaining) continue;  // the tensor ended in an earlier part of this chunk
+    lion_chunk<TP, TM, kMultiUnroll>(static_cast<TP*>(r.p) + off, static_cast<const TP*>(r.g) + off,
+                                      static_cast<TM*>(r.m) + off, r.remaining - off, all_aligned16(r.p, r.g, r.m), c);
   }
 }
 
@@ -234,7 +274,7 @@ struct Plan {
   int device = -1;
   int n_tensors = 0;
   int64_t total_chunks = 0;
-  void* d_blob = nullptr;  // [LionTensor x n][int64 x (n+1)]
+  void* d_blob = nullptr;  // ChunkRecord x total_chunks (the allocation-free entry: [LionTensor x n][int64 x (n+1)])
   uint64_t last_use = 0;   // value of g_plan_clock at the latest call with this list
 };
 
@@ -322,11 +362,23 @@ int64_t one_wave_grid(int device, int64_t total_chunks) {
 }
 
 template <typename TP, typename TM>
-int launch_typed(const Plan& plan, const LionConsts& c, cudaStream_t stream) {
+int launch_records_typed(const Plan& plan, const LionConsts& c, cudaStream_t stream) {
+  const int64_t total_subs = plan.total_chunks * kSubsPerChunk;
+  // the kernel strides over its parts, so a grid cut at the launch limit still covers them all
+  const int64_t grid = total_subs < 0x7fffffffll ? total_subs : 0x7fffffffll;
+  lion_multi_tensor_kernel<TP, TM><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
+      static_cast<const ChunkRecord*>(plan.d_blob), total_subs, c);
+  fo::g_launch_count.fetch_add(1, std::memory_order_relaxed);
+  FO_CUDA_CHECK(cudaGetLastError());
+  return FO_OK;
+}
+
+template <typename TP, typename TM>
+int launch_walk_typed(const Plan& plan, const LionConsts& c, cudaStream_t stream) {
   const LionTensor* tensors = static_cast<const LionTensor*>(plan.d_blob);
   const int64_t* chunk_start = reinterpret_cast<const int64_t*>(tensors + plan.n_tensors);
-  const int64_t grid = one_wave_grid<lion_multi_tensor_kernel<TP, TM>>(plan.device, plan.total_chunks);
-  lion_multi_tensor_kernel<TP, TM><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
+  const int64_t grid = one_wave_grid<lion_table_walk_kernel<TP, TM>>(plan.device, plan.total_chunks);
+  lion_table_walk_kernel<TP, TM><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
       tensors, chunk_start, plan.n_tensors, plan.total_chunks, c);
   fo::g_launch_count.fetch_add(1, std::memory_order_relaxed);
   FO_CUDA_CHECK(cudaGetLastError());
@@ -336,9 +388,10 @@ int launch_typed(const Plan& plan, const LionConsts& c, cudaStream_t stream) {
 template <typename TP, typename TM>
 int launch_single_typed(void* p, const void* g, void* m, int64_t numel, const LionConsts& c, int device,
                         cudaStream_t stream) {
-  constexpr int kElems = kThreads * kVec * SingleUnroll<TP, TM>::value;
+  constexpr int kElems = kThreads * kVec * kSingleUnroll;
   const int64_t total_chunks = (numel + kElems - 1) / kElems;
-  const int64_t grid = one_wave_grid<lion_single_tensor_kernel<TP, TM>>(device, total_chunks);
+  // the kernel strides over chunks, so a grid cut at the launch limit still covers them all
+  const int64_t grid = total_chunks < 0x7fffffffll ? total_chunks : 0x7fffffffll;
   lion_single_tensor_kernel<TP, TM><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
       static_cast<TP*>(p), static_cast<const TP*>(g), static_cast<TM*>(m), numel, total_chunks, c);
   fo::g_launch_count.fetch_add(1, std::memory_order_relaxed);
@@ -357,10 +410,21 @@ int launch_single_typed(void* p, const void* g, void* m, int64_t numel, const Li
   CASE(FO_F32, FO_BF16, float, __nv_bfloat16)          \
   CASE(FO_F32, FO_F16, float, __half)
 
-int launch(const Plan& plan, int p_dtype, int m_dtype, const LionConsts& c, cudaStream_t stream) {
+// `plan.d_blob` holds chunk records.
+int launch_records(const Plan& plan, int p_dtype, int m_dtype, const LionConsts& c, cudaStream_t stream) {
   if (plan.total_chunks == 0) return FO_OK;
 #define FO_LION_CASE(PD, MD, TP, TM) \
-  if (p_dtype == PD && m_dtype == MD) return launch_typed<TP, TM>(plan, c, stream);
+  if (p_dtype == PD && m_dtype == MD) return launch_records_typed<TP, TM>(plan, c, stream);
+  FO_LION_DTYPE_CASES(FO_LION_CASE)
+#undef FO_LION_CASE
+  return fo::fail(FO_ERR_INVALID_ARGUMENT, "unsupported Lion dtype combination p=%d m=%d", p_dtype, m_dtype);
+}
+
+// `plan.d_blob` holds the per-tensor table and its chunk prefix.
+int launch_walk(const Plan& plan, int p_dtype, int m_dtype, const LionConsts& c, cudaStream_t stream) {
+  if (plan.total_chunks == 0) return FO_OK;
+#define FO_LION_CASE(PD, MD, TP, TM) \
+  if (p_dtype == PD && m_dtype == MD) return launch_walk_typed<TP, TM>(plan, c, stream);
   FO_LION_DTYPE_CASES(FO_LION_CASE)
 #undef FO_LION_CASE
   return fo::fail(FO_ERR_INVALID_ARGUMENT, "unsupported Lion dtype combination p=%d m=%d", p_dtype, m_dtype);
@@ -382,20 +446,21 @@ int check_dtypes(int p_dtype, int g_dtype, int m_dtype) {
   return FO_OK;
 }
 
-// Builds the host image of the device table; returns the number of chunks.
-int64_t build_table(void* const* params, const void* const* grads, void* const* exp_avgs,
-                    const int64_t* numels, int n, std::vector<char>* blob) {
-  blob->resize(sizeof(LionTensor) * n + sizeof(int64_t) * (n + 1));
-  LionTensor* tensors = reinterpret_cast<LionTensor*>(blob->data());
-  int64_t* chunk_start = reinterpret_cast<int64_t*>(tensors + n);
+int dtype_size(int dtype) { return dtype == FO_F32 ? 4 : 2; }
+
+// Builds the host image of the chunk records.
+void build_records(void* const* params, const void* const* grads, void* const* exp_avgs, const int64_t* numels,
+                   int n, int p_dtype, int m_dtype, std::vector<ChunkRecord>* records) {
+  const int64_t ps = dtype_size(p_dtype), ms = dtype_size(m_dtype);
   int64_t total = 0;
+  for (int i = 0; i < n; ++i) total += (numels[i] + kChunk - 1) / kChunk;
+  records->clear();
+  records->reserve(static_cast<size_t>(total));
   for (int i = 0; i < n; ++i) {
-    tensors[i] = LionTensor{params[i], grads[i], exp_avgs[i], numels[i]};
-    chunk_start[i] = total;
-    total += (numels[i] + kChunk - 1) / kChunk;
+    for (int64_t off = 0; off < numels[i]; off += kChunk)
+      records->push_back(ChunkRecord{static_cast<char*>(params[i]) + off * ps, static_cast<const char*>(grads[i]) + off * ps,
+                                     static_cast<char*>(exp_avgs[i]) + off * ms, numels[i] - off});
   }
-  chunk_start[n] = total;
-  return total;
 }
 
 }  // namespace
@@ -433,10 +498,14 @@ extern "C" int fo_lion_multi_tensor_step(void* const* params, const void* const*
   if (n == 1)  // no table needed: the tensor travels in the kernel's arguments
     return launch_single(ps[0], gs[0], ms[0], ns[0], p_dtype, m_dtype, c, device, static_cast<cudaStream_t>(stream));
 
-  std::vector<char> blob;
-  const int64_t total = build_table(ps.data(), gs.data(), ms.data(), ns.data(), n, &blob);
+  // key: device, dtypes (the records hold byte addresses) and the raw list
   std::string key(reinterpret_cast<const char*>(&device), sizeof(device));
-  key.append(blob.data(), blob.size());
+  key.append(reinterpret_cast<const char*>(&p_dtype), sizeof(p_dtype));
+  key.append(reinterpret_cast<const char*>(&m_dtype), sizeof(m_dtype));
+  key.append(reinterpret_cast<const char*>(ps.data()), sizeof(void*) * n);
+  key.append(reinterpret_cast<const char*>(gs.data()), sizeof(void*) * n);
+  key.append(reinterpret_cast<const char*>(ms.data()), sizeof(void*) * n);
+  key.append(reinterpret_cast<const char*>(ns.data()), sizeof(int64_t) * n);
 
   // The lock is held across the launch: a table can then not be evicted (by another thread's
   // new list) between the lookup and the moment its kernel is in the stream, and cudaFree does
@@ -453,23 +522,26 @@ extern "C" int fo_lion_multi_tensor_step(void* const* params, const void* const*
                       "that the device table exists");
     // A caller whose pointers change every step would grow the cache without bound.
     if (g_plans.size() >= kMaxPlans) evict_oldest_plan_locked();
+    std::vector<ChunkRecord> records;
+    build_records(ps.data(), gs.data(), ms.data(), ns.data(), n, p_dtype, m_dtype, &records);
     Plan plan;
     plan.device = device;
     plan.n_tensors = n;
-    plan.total_chunks = total;
-    FO_CUDA_CHECK(cudaMalloc(&plan.d_blob, blob.size()));
+    plan.total_chunks = static_cast<int64_t>(records.size());
+    const size_t bytes = records.size() * sizeof(ChunkRecord);
+    FO_CUDA_CHECK(cudaMalloc(&plan.d_blob, bytes));
     // On the caller's stream, so that the copy and the kernel below are ordered whatever kind of
     // stream it is.  The source is pageable: the runtime has staged it when the call returns,
     // so the host image may die with this call.
-    cudaError_t e = cudaMemcpyAsync(plan.d_blob, blob.data(), blob.size(), cudaMemcpyHostToDevice, s);
+    cudaError_t e = cudaMemcpyAsync(plan.d_blob, records.data(), bytes, cudaMemcpyHostToDevice, s);
     if (e != cudaSuccess) {
       cudaFree(plan.d_blob);
-      return fo::fail(FO_ERR_CUDA, "tensor table upload failed: %s", cudaGetErrorString(e));
+      return fo::fail(FO_ERR_CUDA, "chunk record upload failed: %s", cudaGetErrorString(e));
     }
     it = g_plans.emplace(std::move(key), plan).first;
   }
   it->second.last_use = ++g_plan_clock;
-  return launch(it->second, p_dtype, m_dtype, c, s);
+  return launch_records(it->second, p_dtype, m_dtype, c, s);
 }
 
 extern "C" int fo_lion_clear_cache(void) {
@@ -618,7 +690,7 @@ extern "C" int fo_lion_multi_tensor_step_noalloc(void* const* params, const void
   plan.n_tensors = n;
   plan.total_chunks = total;
   plan.d_blob = d_table;
-  return launch(plan, p_dtype, m_dtype, c, s);
+  return launch_walk(plan, p_dtype, m_dtype, c, s);
 }
 
 // ---- ZeRO-1 step fused with the distribution of the updated weights ---------------------------

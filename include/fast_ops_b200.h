@@ -178,12 +178,13 @@ int fo_lion_update(void* param, const void* grad, void* exp_avg, int64_t numel,
  * The same step over a list of tensors in ONE kernel launch.  Replaces the
  * per-tensor loop of Lion.step() (fast_ops/lion/lion_optimizer.py:57-76).
  * `params`, `grads`, `exp_avgs` and `numels` are HOST arrays of n_tensors
- * entries holding device pointers / element counts.  The device-side tensor
- * table is built on the first call for a given list (cudaMalloc, and a copy on
- * `stream`) and cached inside the library, keyed by the list's contents, so
- * later calls with the same list do no host-to-device copy.  At most 32 lists
- * are kept; the least recently used one is dropped for a new one.  A list of
- * one tensor needs no table.  CUDA graphs: a captured launch keeps its list's
+ * entries holding device pointers / element counts.  The device-side table
+ * (one 32-byte record per 8192 elements of every tensor: 0.4 % of the bytes of
+ * a 16-bit tensor) is built on the first call for a given list and dtypes
+ * (cudaMalloc, and a copy on `stream`) and cached inside the library, keyed by
+ * the list's contents, so later calls with the same list do no host-to-device
+ * copy.  At most 32 lists are kept; the least recently used one is dropped for
+ * a new one.  A list of one tensor needs no table.  CUDA graphs: a captured launch keeps its list's
  * table, so make the first call with a list outside the capture (on a capturing
  * stream it is refused with FO_ERR_UNSUPPORTED), and neither 32 other lists nor
  * fo_lion_clear_cache may come between the capture and a replay.
