@@ -156,46 +156,22 @@ class Dist:
             self.dist.destroy_process_group()
 
 
-_flush_buf = None
-
-
-def flush_l2(device):
-    """Overwrites a 512 MB buffer (four times the 126 MB L2)."""
-    global _flush_buf
-    if _flush_buf is None or _flush_buf.device != device:
-        _flush_buf = torch.empty(512 << 20, dtype=torch.uint8, device=device)
-    _flush_buf.zero_()
-
-
-def timed_steps(d: Dist, fn, steps: int, warmup: int, sampler=None, flush=False):
+def timed_steps(d: Dist, fn, steps: int, warmup: int, sampler=None):
     """W untimed steps, then exactly K steps between a barrier + synchronize on both sides;
     CUDA events on the launching (current) stream; returns the max over ranks of ms per step.
-    With `flush`, L2 is overwritten before every step and each step has its own event pair
-    (the flush is outside the events)."""
+    Callers give `fn` inputs larger than L2, or several input sets that it uses in turn."""
     for _ in range(warmup):
         fn()
     d.barrier()
     if sampler:
         sampler.start()
-    if flush:
-        pairs = []
-        for _ in range(steps):
-            flush_l2(d.device)
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            fn()
-            e1.record()
-            pairs.append((e0, e1))
-        d.barrier()
-        total = sum(a.elapsed_time(b) for a, b in pairs)
-    else:
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
-            fn()
-        e1.record()
-        d.barrier()
-        total = e0.elapsed_time(e1)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    d.barrier()
+    total = e0.elapsed_time(e1)
     clocks = sampler.stop() if sampler else None
     return d.max_ms(total) / steps, clocks
 
@@ -219,11 +195,20 @@ def attention_config(name: str, world: int, split: str):
     heads = B * H // world if strong else B * H
     where = (f"the {B * H} (batch, head) pairs split {heads} per GPU over {world} GPUs" if strong else "per GPU")
     input_bytes = 3 * heads * S * D * 2
-    flush = input_bytes <= 2 * 126e6
+    sets = rotating_sets(input_bytes)
     return {"workload": f"{name}: attention fwd B={B} H={H} S={S} D={D} bf16 causal={causal}, {where}",
             "global_batch": B if strong else B * world,
-            "l2": ("L2 flushed (512 MB written) before every timed step" if flush
-                   else "inputs (%.0f MB) larger than L2, no flush" % (input_bytes / 1e6))}
+            "l2": ("%d input sets used in turn (%.0f MB in total, larger than L2), no flush" % (sets, sets * input_bytes / 1e6)
+                   if sets > 1 else "inputs (%.0f MB) larger than L2, no flush" % (input_bytes / 1e6))}
+
+
+def rotating_sets(input_bytes: float) -> int:
+    """How many distinct input sets a timed loop cycles through so that a set has left L2 (126 MB)
+    before it is read again: one when a single set is already larger than twice L2, else enough
+    sets for three times L2 between two uses of the same one."""
+    if input_bytes > 2 * 126e6:
+        return 1
+    return int(-(-3 * 126e6 // input_bytes)) + 1
 
 
 def bench_attention(d: Dist, name: str, steps: int, warmup: int, peaks, with_e2e=True, with_clocks=True,
@@ -249,12 +234,22 @@ def bench_attention(d: Dist, name: str, steps: int, warmup: int, peaks, with_e2e
         flops_rank, flops_job = flops_shape, flops_shape * d.world
     q, k, v = attn_inputs(Bl, Hl, S, D, d.device, seed=1000 + d.rank)
     lib = L.load()
-    fn = lambda: flash_attention_forward(q, k, v, causal=causal)  # noqa: E731
+    # a shape smaller than L2 is timed on several input sets used in turn, back to back like the
+    # large ones, so that every launch reads its inputs from HBM
+    sets = [(q, k, v)]
+    for i in range(1, rotating_sets(3 * q.numel() * 2)):
+        sets.append(attn_inputs(Bl, Hl, S, D, d.device, seed=1000 + d.rank + 100 * i))
+    turn = [0]
+
+    def fn():
+        a, b, c = sets[turn[0] % len(sets)]
+        turn[0] += 1
+        return flash_attention_forward(a, b, c, causal=causal)
+
     launches0 = lib.fo_launch_count()
     sampler = ClockSampler(d.local_rank) if with_clocks else None
-    input_bytes = 3 * q.numel() * 2
-    flush = input_bytes <= 2 * 126e6
-    ms, clocks = timed_steps(d, fn, steps, warmup, sampler, flush=flush)
+    ms, clocks = timed_steps(d, fn, steps, warmup, sampler)
+    del sets
     launches = (lib.fo_launch_count() - launches0 - warmup)
     if L.device_status(d.local_rank) != 0:
         raise RuntimeError("an attention kernel reported a timed-out wait")

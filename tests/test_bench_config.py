@@ -30,8 +30,8 @@ def test_strong_split_covers_every_pair_once():
         else:
             assert cfg["workload"].endswith("per GPU") and cfg["global_batch"] == B
         # L2 note: inputs of a rank against twice the L2
-        flush = 3 * per_rank * S * D * 2 <= 2 * 126e6
-        assert ("flushed" in cfg["l2"]) == flush
+        small = 3 * per_rank * S * D * 2 <= 2 * 126e6
+        assert ("input sets used in turn" in cfg["l2"]) == small
     # the weak form multiplies the batch instead
     assert bench.attention_config("attn_c3", 8, "weak")["global_batch"] == 8 * B
 
