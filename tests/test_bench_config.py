@@ -60,3 +60,15 @@ def test_reference_arm_prints_the_gpu_arms_config():
     out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "2"],
                          capture_output=True, text=True, env=dict(os.environ, RANK="1"), timeout=60)
     assert out.returncode == 0 and out.stdout.strip() == ""
+
+
+def test_rotating_input_sets_cover_three_times_l2():
+    bench = load_bench()
+    l2 = 126e6
+    assert bench.rotating_sets(805e6) == 1 and bench.rotating_sets(2 * l2 + 1) == 1
+    for nbytes in (50.3e6, 100.7e6, 2 * l2):
+        sets = bench.rotating_sets(nbytes)
+        assert sets >= 2
+        # between two uses of one set, the other sets alone push at least three times L2 through it
+        assert (sets - 1) * nbytes >= 3 * l2
+        assert (sets - 2) * nbytes < 3 * l2  # and not one set more than that needs
