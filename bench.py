@@ -13,8 +13,8 @@ step on the GPT-2-medium list and, sharded ZeRO-1 style, on the Llama-7B list).
 `cpu_baseline` times the CPU oracle (a C restatement of the reference's torch code) on a
 bounded sample of the same workload.  `--impl reference` runs only that CPU arm.
 
-Workloads: attn_c3 (default), attn_c2, attn_bwd_c3, lion_c4, lion_c5 (attn_prof and attn_bwd_prof are
-the small shapes used for profiler captures).
+Workloads: attn_c3 (default), attn_c2, attn_bwd_c3, lion_c4, lion_c5 (attn_prof, attn_short_prof and
+attn_bwd_prof are the small shapes used for profiler captures).
 Launch under torchrun for N > 1 (one rank per GPU); inputs are synthetic and seeded.
 """
 from __future__ import annotations
@@ -38,6 +38,7 @@ ATTN = {
     "attn_c2": (8, 12, 1024, 64, True),
     "attn_c3": (2, 32, 16384, 128, True),
     "attn_prof": (2, 32, 4096, 128, True),  # small case for profiler captures (inputs 201 MB > L2)
+    "attn_short_prof": (32, 32, 1024, 128, True),  # the same for the one-tile-per-CTA kernel (805 MB)
 }
 
 
@@ -733,7 +734,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", default="attn_c3",
-                    choices=["attn_c3", "attn_c2", "attn_prof", "attn_bwd_c3", "attn_bwd_prof", "lion_c4", "lion_c5"])
+                    choices=["attn_c3", "attn_c2", "attn_prof", "attn_short_prof", "attn_bwd_c3", "attn_bwd_prof", "lion_c4", "lion_c5"])
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-also", action="store_true", help="skip the secondary workloads")
