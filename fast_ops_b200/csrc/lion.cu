@@ -232,8 +232,8 @@ lion_single_tensor_kernel(TP* __restrict__ p, const TP* __restrict__ g, TM* __re
 
 // One launch covers all tensors, described by one record per CHUNK of kChunk elements (pointers
 // already advanced to the chunk, and how many elements are left of its tensor from there on): a
-// CTA needs one 32-byte load to know its work, so the launch can use one CTA per quarter chunk
-// like the single-tensor kernel instead of a resident wave that walks a tensor table.  The
+// CTA needs one 32-byte load to know its work, so the launch can use one CTA per quarter or half
+// chunk like the single-tensor kernel instead of a resident wave that walks a tensor table.  The
 // records cost 32 bytes of device memory and of traffic per kChunk elements (0.05 % of the
 // step's traffic with 16-bit tensors).
 struct ChunkRecord {
@@ -244,26 +244,31 @@ struct ChunkRecord {
 };
 static_assert(sizeof(ChunkRecord) == 32, "two 16-byte loads");
 
-// One group per thread, as in the single-tensor kernel.  Measured, one CTA per 2048 / 4096 / 8192
-// elements: GPT-2-medium list (fp32 p, g) 6.94 / 6.83 / 6.89 TB/s, a list of 64 bf16 matrices of
-// 4096 x 11008 6.39 / 6.65 / 6.50.
-constexpr int kMultiUnroll = 1;
-constexpr int kSubElems = kThreads * kVec * kMultiUnroll;  // elements of one CTA
-constexpr int kSubsPerChunk = kChunk / kSubElems;
-static_assert(kChunk % kSubElems == 0 && kSubElems % 8 == 0, "a CTA's part starts 16-byte aligned whenever the tensor does");
+// Groups per thread.  Measured, one CTA per 2048 / 4096 / 8192 elements: GPT-2-medium list (fp32
+// p, g) 6.94 / 6.83 / 6.89 TB/s, a list of 64 bf16 matrices of 4096 x 11008 6.39 / 6.65 / 6.50:
+// with 16-bit parameters a CTA of one group moves 20 KB for its one dependent record load, with
+// 32-bit ones 32 KB, so the former take two groups.
+template <typename TP> struct MultiShape {
+  static constexpr int kUnroll = sizeof(TP) == 2 ? 2 : 1;
+  static constexpr int kSubElems = kThreads * kVec * kUnroll;  // elements of one CTA
+  static constexpr int kSubsPerChunk = kChunk / kSubElems;
+  static_assert(kChunk % kSubElems == 0 && kSubElems % 8 == 0,
+                "a CTA's part starts 16-byte aligned whenever the tensor does");
+};
 
 template <typename TP, typename TM>
 __global__ void __launch_bounds__(kThreads)
 lion_multi_tensor_kernel(const ChunkRecord* __restrict__ records, int64_t total_subs, LionConsts c) {
   for (int64_t sub = blockIdx.x; sub < total_subs; sub += gridDim.x) {
-    const uint4* rp = reinterpret_cast<const uint4*>(records + sub / kSubsPerChunk);
+    using Shape = MultiShape<TP>;
+    const uint4* rp = reinterpret_cast<const uint4*>(records + sub / Shape::kSubsPerChunk);
     const uint4 lo = __ldg(rp), hi = __ldg(rp + 1);
     ChunkRecord r;
     memcpy(&r, &lo, 16);
     memcpy(reinterpret_cast<char*>(&r) + 16, &hi, 16);
-    const int64_t off = (sub % kSubsPerChunk) * static_cast<int64_t>(kSubElems);
+    const int64_t off = (sub % Shape::kSubsPerChunk) * static_cast<int64_t>(Shape::kSubElems);
     if (off >= r.remaining) continue;  // the tensor ended in an earlier part of this chunk
-    lion_chunk<TP, TM, kMultiUnroll>(static_cast<TP*>(r.p) + off, static_cast<const TP*>(r.g) + off,
+    lion_chunk<TP, TM, Shape::kUnroll>(static_cast<TP*>(r.p) + off, static_cast<const TP*>(r.g) + off,
                                       static_cast<TM*>(r.m) + off, r.remaining - off, all_aligned16(r.p, r.g, r.m), c);
   }
 }
@@ -363,7 +368,7 @@ int64_t one_wave_grid(int device, int64_t total_chunks) {
 
 template <typename TP, typename TM>
 int launch_records_typed(const Plan& plan, const LionConsts& c, cudaStream_t stream) {
-  const int64_t total_subs = plan.total_chunks * kSubsPerChunk;
+  const int64_t total_subs = plan.total_chunks * MultiShape<TP>::kSubsPerChunk;
   // the kernel strides over its parts, so a grid cut at the launch limit still covers them all
   const int64_t grid = total_subs < 0x7fffffffll ? total_subs : 0x7fffffffll;
   lion_multi_tensor_kernel<TP, TM><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
